@@ -1,12 +1,15 @@
 """The cache manager: device buffers, page groups, state slots, per-request holdings.
 
 It is built from the cache needs of a model's run entries (``PagedKV`` /
-``FixedState`` / none) and nothing else about the model.
+``FixedState`` / none, or a tuple of these for a mixer that keeps several things) and
+nothing else about the model.  Needs beyond the run order (the embedding's, if it keeps
+something per request) follow as further entries.
 
 Paged groups.  Entries that need all keys and entries that need a window of them are
 different groups: each group has its own page pool and its own block table per request,
 so a window group can give pages back as the window passes them while the other keeps
-everything.  Within a group every entry has its own K and V buffer
+everything.  Entries that hold one row per run of ``every`` positions (summaries of
+blocks) form groups of their own as well, with a pool sized for that many fewer rows.  Within a group every entry has its own K and V buffer
 ``[num_pages, page_size, kv_heads, head_dim]`` (widths may differ between entries); a
 page id names the same rows in all of them, as the reference's pages do
 (crates/shiso-engine/src/kv.rs:18-31,97-109).
@@ -53,10 +56,22 @@ class FixedStateView:
 
 
 class _Group:
-    def __init__(self, index: int, window: Optional[int], num_pages: int):
+    def __init__(self, index: int, window: Optional[int], every: int, num_pages: int, scratch_pages: int):
         self.index = index
         self.window = window
+        self.every = every
+        self.num_pages = num_pages
         self.pool = PagePool(num_pages)
+        self.scratch_pages = list(range(num_pages, num_pages + scratch_pages))  # behind the pool, held by nobody
+
+
+def flat_needs(need) -> list:
+    """The needs of one entry as a list: none, one, or the members of a tuple."""
+    if need is None:
+        return []
+    if isinstance(need, (tuple, list)):
+        return [n for n in need if n is not None]
+    return [need]
 
 
 class _Held:
@@ -91,23 +106,29 @@ class CacheManager:
         self.device = torch.device(device)
         self.needs = list(needs)
         scratch_pages = -(-scratch_tokens // page_size) if scratch_tokens > 0 else 0
-        self.scratch_pages = list(range(num_pages, num_pages + scratch_pages))
         self.scratch_slot = num_slots if scratch_tokens > 0 else None
-        buffer_pages = num_pages + scratch_pages
         self.groups: list[_Group] = []
         self._views: list = [None] * len(needs)
-        by_window: dict = {}
-        for pos, need in enumerate(needs):
-            if isinstance(need, PagedKV):
+        by_kind: dict = {}
+        built: dict = {}  # (entry, index within the entry) -> view
+        for pos, entry in enumerate(needs):
+            for j, need in enumerate(flat_needs(entry)):
+                if not isinstance(need, PagedKV):
+                    continue
                 if need.window is not None and need.window <= 0:
                     raise ValueError(f"run entry {pos}: window {need.window} must be positive")
-                if need.window not in by_window:
-                    group = _Group(len(self.groups), need.window, num_pages)
-                    self.groups.append(group)
-                    by_window[need.window] = group
-                group = by_window[need.window]
+                if need.every < 1:
+                    raise ValueError(f"run entry {pos}: one row per {need.every} positions is not possible")
+                kind = (need.window, need.every)
+                if kind not in by_kind:
+                    # rows per request round down to whole runs, pages round up per request
+                    pages = num_pages if need.every == 1 else -(-num_pages // need.every) + num_slots
+                    by_kind[kind] = _Group(len(self.groups), need.window, need.every, pages, scratch_pages)
+                    self.groups.append(by_kind[kind])
+                group = by_kind[kind]
+                buffer_pages = group.num_pages + scratch_pages
                 kv_dtype = need.dtype if need.dtype is not None else dtype
-                self._views[pos] = PagedKVView(
+                built[(pos, j)] = PagedKVView(
                     k=torch.zeros((buffer_pages, page_size, need.num_kv_heads, need.head_dim), dtype=kv_dtype, device=self.device),
                     v=torch.zeros((buffer_pages, page_size, need.num_kv_heads, need.value_dim), dtype=kv_dtype, device=self.device),
                     page_size=page_size,
@@ -116,22 +137,29 @@ class CacheManager:
                     head_dim=need.head_dim,
                 )
         self.num_pages = num_pages
+        self.scratch_pages = list(range(num_pages, num_pages + scratch_pages))  # of the groups with a row per position
         self.max_blocks = max_blocks_per_request or num_pages
 
         # Fixed-size state: one row of bytes per slot, one aligned column range per entry.
         offsets, total = {}, 0
-        for pos, need in enumerate(needs):
-            if isinstance(need, FixedState):
-                offsets[pos] = total
-                total += -(-need.nbytes // 16) * 16
+        for pos, entry in enumerate(needs):
+            for j, need in enumerate(flat_needs(entry)):
+                if isinstance(need, FixedState):
+                    offsets[(pos, j)] = (total, need)
+                    total += -(-need.nbytes // 16) * 16
         self.bytes_per_slot = total
         self.slots = SlotPool(num_slots)
         self.num_slots = num_slots
         self.state = torch.zeros((num_slots + (1 if scratch_tokens > 0 else 0), max(total, 16)), dtype=torch.uint8, device=self.device)
-        for pos, off in offsets.items():
-            need = needs[pos]
+        for key, (off, need) in offsets.items():
             view = self.state[:, off : off + need.nbytes].view(need.dtype).unflatten(1, need.shape)
-            self._views[pos] = FixedStateView(state=view)
+            built[key] = FixedStateView(state=view)
+        for pos, entry in enumerate(needs):
+            members = flat_needs(entry)
+            if isinstance(entry, (tuple, list)):
+                self._views[pos] = tuple(built[(pos, j)] for j in range(len(members)))
+            elif members:
+                self._views[pos] = built[(pos, 0)]
 
         self._held: dict = {}
 
@@ -141,10 +169,11 @@ class CacheManager:
         pool's sizing needs to know about a model (the reference prices pages run by run the
         same way, crates/shiso-engine/src/kv.rs:26-31,84-109,176-198)."""
         page_bytes = state_bytes = 0
-        for need in needs:
+        for need in (n for entry in needs for n in flat_needs(entry)):
             if isinstance(need, PagedKV):
                 itemsize = (need.dtype if need.dtype is not None else dtype).itemsize
-                page_bytes += page_size * need.num_kv_heads * (need.head_dim + need.value_dim) * itemsize
+                # (an entry with a row per run of positions costs that much less per page of tokens)
+                page_bytes += -(-page_size * need.num_kv_heads * (need.head_dim + need.value_dim) * itemsize // need.every)
             elif isinstance(need, FixedState):
                 state_bytes += -(-need.nbytes // 16) * 16
         return page_bytes, state_bytes
@@ -156,9 +185,17 @@ class CacheManager:
         view = self._views[entry]
         if view is None or owner:
             return view
-        if isinstance(view, PagedKVView):
-            return PagedKVView(view.k, view.v, view.page_size, view.group, view.kv_heads, view.head_dim, owner=False)
-        return FixedStateView(view.state, owner=False)
+
+        def borrowed(v):
+            if isinstance(v, PagedKVView):
+                return PagedKVView(v.k, v.v, v.page_size, v.group, v.kv_heads, v.head_dim, owner=False)
+            return FixedStateView(v.state, owner=False)
+
+        return tuple(borrowed(v) for v in view) if isinstance(view, tuple) else borrowed(view)
+
+    def scratch_pages_of(self, group: int) -> list:
+        """The pages behind group ``group``'s pool that the made-up rows of a padded step use."""
+        return self.groups[group].scratch_pages
 
     # ------------------------------------------------------------------ requests
 
@@ -177,7 +214,7 @@ class CacheManager:
         out = []
         for group in self.groups:
             if held is None:
-                out.append(-(-n_tokens // self.page_size))
+                out.append(-(-(n_tokens // group.every) // self.page_size))
             else:
                 out.append(held.tables[group.index].missing_for(held.length + n_tokens))
         return out
@@ -213,7 +250,7 @@ class CacheManager:
             slot = self.slots.take()  # raises OutOfPages before anything else is taken
             if self.bytes_per_slot:
                 self.state[slot].zero_()
-            held = _Held([BlockTable(self.page_size, g.window) for g in self.groups], slot)
+            held = _Held([BlockTable(self.page_size, g.window, g.every) for g in self.groups], slot)
             self._held[request] = held
         for group in self.groups:
             held.tables[group.index].grow(group.pool, held.length + n_tokens)

@@ -84,15 +84,16 @@ HOLE = -1  # a block-table entry whose page went back to the pool (the window pa
 class BlockTable:
     """One request's pages in one group, in position order."""
 
-    def __init__(self, page_size: int, window: int | None = None):
+    def __init__(self, page_size: int, window: int | None = None, every: int = 1):
         self.page_size = page_size
         self.window = window
+        self.every = every  # one row per complete run of this many positions
         self.pages: list[int] = []
         self.first_live = 0  # entries below this index are holes
         self._array = np.empty(16, dtype=np.int32)  # the same entries, ready to be copied into a step's table
 
     def pages_for(self, length: int) -> int:
-        return -(-length // self.page_size)
+        return -(-(length // self.every) // self.page_size)
 
     def missing_for(self, length: int) -> int:
         return max(0, self.pages_for(length) - len(self.pages))
@@ -119,7 +120,7 @@ class BlockTable:
         query at position ``length`` (the next one) reads positions ``> length - w``."""
         if self.window is None:
             return 0
-        first_needed = max(0, length + 1 - self.window)
+        first_needed = max(0, length + 1 - self.window) // self.every
         keep_from = first_needed // self.page_size
         released = 0
         while self.first_live < min(keep_from, len(self.pages)):

@@ -12,12 +12,15 @@ from .registry import (
     unregister_architecture,
 )
 from . import lfm2  # registers Lfm2ForCausalLM
+from . import filulix  # registers Filulix
+from .filulix import FilulixConfig
 from .lfm2 import Lfm2Config, feed_forward_width
 
 __all__ = [
     "Architecture",
     "ConfigError",
     "ConfigMissing",
+    "FilulixConfig",
     "InvalidValue",
     "Lfm2Config",
     "UnknownArchitecture",

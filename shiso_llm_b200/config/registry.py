@@ -1,7 +1,7 @@
 """One registry from an architecture's name to its configuration and plan.
 
-``config.json`` names the model class in ``architectures[0]``; that string is
-the key.  An entry holds the typed configuration class (which reads the
+``config.json`` names the model class in ``architectures[0]`` (or, in documents that
+name one class only, in the string ``architecture``); that string is the key.  An entry holds the typed configuration class (which reads the
 architecture's own config.json keys) and a function that turns a configuration
 into a ``ModelPlan``.  The reference resolves a family with a chain of
 ``Family::describes(config)`` arms that ends in ``UnknownArchitecture``
@@ -56,6 +56,14 @@ def architecture_of(document: Mapping[str, Any]) -> Architecture:
         arch = _ARCHITECTURES.get(names[0])
         if arch is None:
             raise UnknownArchitecture(names[0], registered_architectures())
+        return arch
+    single = document.get("architecture")
+    if single is not None:
+        if not isinstance(single, str) or not single:
+            raise InvalidValue("architecture", single, "expected a name")
+        arch = _ARCHITECTURES.get(single)
+        if arch is None:
+            raise UnknownArchitecture(single, registered_architectures())
         return arch
     model_type = document.get("model_type")
     if model_type is None:

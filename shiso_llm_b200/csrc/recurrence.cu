@@ -1,0 +1,212 @@
+// Linear recurrences with a matrix state per head, walked token by token in float.
+//
+// One CTA per (head, sequence) holds the head's state S[key, value] in registers and walks the
+// sequence's rows of this step in order, so a position's output does not depend on how the
+// sequence was cut into steps or on what else is in the batch.  Two forms:
+//
+//   channel decay (time mixing of the RWKV family)
+//       w_t = exp(-exp(logit_t + bias))                       per key channel
+//       o_t = (S_{t-1} + diag(bonus) k_t v_t^T)^T q_t
+//       S_t = diag(w_t) S_{t-1} + k_t v_t^T
+//   head decay (retention)
+//       q_t, k_t rotated by the position (half-split pairs), k_t times key_scale
+//       S_t = decay_h S_{t-1} + k_t v_t^T
+//       o_t = S_t^T q_t
+//
+// then, for both, o_t brought to unit RMS over the head's value channels, times an optional
+// weight, times silu(gate), times a constant, rounded to the activation type.
+//
+// Thread layout: a value column j of the state belongs to SPLIT neighbouring lanes, each
+// holding the rows i = ii * SPLIT + part in registers; the SPLIT partial sums of o_j meet in
+// two shuffles.  q, k and the decays of a token are staged in shared memory (two buffers, so
+// one barrier per token for them and one for the RMS).
+#include "common.cuh"
+
+constexpr int REC_MAX_DIM = 256;
+constexpr int REC_MAX_STATE = 32768;  // floats of one head's state: what a CTA keeps in registers
+
+struct RecurrenceArgs {
+    const void* q; const void* k; const void* v; const void* gate;
+    long long q_ld, k_ld, v_ld, gate_ld, out_ld;
+    void* out;
+    float* state; long long state_stride;  // [slots][heads][dim][vdim], slots `state_stride` floats apart
+    const int* q_start; const int* slots; const int* positions;
+    const float* decay_logits; long long logits_ld; const float* decay_bias; const float* bonus;  // channel decay
+    const float* head_decay; const float* inv_freq; int rotary_dim; float key_scale;               // head decay
+    const float* out_weight;
+    float eps, out_scale;
+    int heads, dim, vdim;
+};
+
+// Threads a CTA may have so that RPT rows of the state (and what else a thread needs) stay in registers.
+constexpr int rec_max_threads(int rpt) { return rpt <= 32 ? 512 : (rpt <= 128 ? 256 : 128); }
+
+template <typename AT, int RPT, int SPLIT, bool CHANNEL>
+__global__ void __launch_bounds__(rec_max_threads(RPT)) decay_recurrence_kernel(const RecurrenceArgs a) {
+    __shared__ float sq[2][REC_MAX_DIM], sk[2][REC_MAX_DIM], sw[2][REC_MAX_DIM], su[REC_MAX_DIM];
+    __shared__ float red[2][32];
+    const int head = blockIdx.x, seq = blockIdx.y;
+    const int tid = threadIdx.x;
+    const int j = tid / SPLIT, part = tid % SPLIT;
+    const int dim = a.dim, vdim = a.vdim;
+    const int rpt = dim / SPLIT;  // rows of the state per thread (dim is a multiple of SPLIT)
+    const bool owns = j < vdim;
+    const int lane = tid & 31, warp = tid >> 5, nwarps = (blockDim.x + 31) >> 5;
+
+    if (CHANNEL)
+        for (int c = tid; c < dim; c += blockDim.x) su[c] = a.bonus[head * dim + c];
+    const float head_decay = CHANNEL ? 0.0f : a.head_decay[head];
+    pdl_wait();
+    const int first = a.q_start[seq], last = a.q_start[seq + 1];
+    if (last <= first) return;
+    float* state = a.state + (long long)a.slots[seq] * a.state_stride + (size_t)head * dim * vdim;
+    float S[RPT];
+#pragma unroll
+    for (int ii = 0; ii < RPT; ++ii) S[ii] = (owns && ii < rpt) ? state[(size_t)(ii * SPLIT + part) * vdim + j] : 0.0f;
+
+    const AT* q = (const AT*)a.q + (size_t)head * dim;
+    const AT* k = (const AT*)a.k + (size_t)head * dim;
+    const AT* v = (const AT*)a.v + (size_t)head * vdim;
+    const AT* gate = a.gate ? (const AT*)a.gate + (size_t)head * vdim : nullptr;
+    AT* out = (AT*)a.out + (size_t)head * vdim;
+    const int half = a.rotary_dim / 2;
+
+    for (int t = first; t < last; ++t) {
+        const int b = (t - first) & 1;
+        for (int c = tid; c < dim; c += blockDim.x) {
+            float qc = to_f32(q[(size_t)t * a.q_ld + c]);
+            float kc = to_f32(k[(size_t)t * a.k_ld + c]);
+            if (!CHANNEL) {
+                if (c < a.rotary_dim) {
+                    const int pair = c < half ? c : c - half;
+                    const int other = c < half ? c + half : c - half;
+                    float sn, cs;
+                    sincosf((float)a.positions[t] * a.inv_freq[pair], &sn, &cs);
+                    const float qo = to_f32(q[(size_t)t * a.q_ld + other]), ko = to_f32(k[(size_t)t * a.k_ld + other]);
+                    qc = c < half ? qc * cs - qo * sn : qc * cs + qo * sn;
+                    kc = c < half ? kc * cs - ko * sn : kc * cs + ko * sn;
+                }
+                kc *= a.key_scale;
+            } else {
+                sw[b][c] = expf(-expf(a.decay_logits[(size_t)t * a.logits_ld + head * dim + c] + a.decay_bias[head * dim + c]));
+            }
+            sq[b][c] = qc;
+            sk[b][c] = kc;
+        }
+        const float vj = owns ? to_f32(v[(size_t)t * a.v_ld + j]) : 0.0f;
+        __syncthreads();
+        float o = 0.0f;
+#pragma unroll
+        for (int ii = 0; ii < RPT; ++ii) {
+            if (ii < rpt) {
+                const int i = ii * SPLIT + part;
+                const float kv = sk[b][i] * vj;
+                if (CHANNEL) {
+                    o += sq[b][i] * (S[ii] + su[i] * kv);
+                    S[ii] = sw[b][i] * S[ii] + kv;
+                } else {
+                    S[ii] = head_decay * S[ii] + kv;
+                    o += sq[b][i] * S[ii];
+                }
+            }
+        }
+#pragma unroll
+        for (int off = 1; off < SPLIT; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
+        const float mine = (owns && part == 0) ? o * o : 0.0f;
+        const float partial = warp_sum(mine);
+        if (lane == 0) red[b][warp] = partial;
+        __syncthreads();
+        float squares = 0.0f;
+        for (int w = 0; w < nwarps; ++w) squares += red[b][w];
+        if (owns && part == 0) {
+            float y = o * rsqrtf(squares / (float)vdim + a.eps);
+            if (a.out_weight) y *= a.out_weight[head * vdim + j];
+            if (gate) {
+                const float g = to_f32(gate[(size_t)t * a.gate_ld + j]);
+                y *= g / (1.0f + expf(-g));
+            }
+            out[(size_t)t * a.out_ld + j] = from_f32<AT>(y * a.out_scale);
+        }
+    }
+    pdl_trigger();
+#pragma unroll
+    for (int ii = 0; ii < RPT; ++ii)
+        if (owns && ii < rpt) state[(size_t)(ii * SPLIT + part) * vdim + j] = S[ii];
+}
+
+template <typename AT, int SPLIT, bool CHANNEL>
+static int launch_recurrence(const RecurrenceArgs& a, int num_seqs, cudaStream_t stream) {
+    const int rpt = a.dim / SPLIT;
+    const unsigned threads = (unsigned)((a.vdim * SPLIT + 31) / 32 * 32);
+    const dim3 grid(a.heads, num_seqs);
+#define SHISO_REC(R)                                                                                          \
+    if constexpr (R * SPLIT <= REC_MAX_DIM) {                                                                 \
+        if (rpt <= R) {                                                                                       \
+            if (threads > (unsigned)rec_max_threads(R)) return SHISO_ERR_SHAPE;                               \
+            launch_kernel(decay_recurrence_kernel<AT, R, SPLIT, CHANNEL>, grid, threads, 0, stream, a);       \
+            return launch_status();                                                                           \
+        }                                                                                                     \
+    }
+    SHISO_REC(8) SHISO_REC(16) SHISO_REC(32) SHISO_REC(64) SHISO_REC(128) SHISO_REC(256)
+#undef SHISO_REC
+    return SHISO_ERR_SHAPE;
+}
+
+static int rows_bucket(int rpt) {
+    for (int r = 8; r <= REC_MAX_DIM; r *= 2)
+        if (rpt <= r) return r;
+    return REC_MAX_DIM;
+}
+
+// Into how many lanes a column of the state is split: as many (4, 2, 1) as divide the key size
+// and leave the CTA within the threads its rows per thread allow; 0 when nothing fits.
+static int choose_split(int dim, int vdim) {
+    for (int split = 4; split >= 1; split /= 2) {
+        if (dim % split || dim / split < 1) continue;
+        const int threads = (vdim * split + 31) / 32 * 32;
+        if (threads <= rec_max_threads(rows_bucket(dim / split))) return split;
+    }
+    return 0;
+}
+
+SHISO_API int shiso_decay_recurrence_supported(int dim, int vdim) {
+    return dim > 0 && vdim > 0 && dim <= REC_MAX_DIM && vdim <= REC_MAX_DIM && dim * vdim <= REC_MAX_STATE && choose_split(dim, vdim) > 0;
+}
+
+template <typename AT, bool CHANNEL>
+static int pick_split(const RecurrenceArgs& a, int num_seqs, cudaStream_t stream) {
+    switch (choose_split(a.dim, a.vdim)) {
+        case 4: return launch_recurrence<AT, 4, CHANNEL>(a, num_seqs, stream);
+        case 2: return launch_recurrence<AT, 2, CHANNEL>(a, num_seqs, stream);
+        case 1: return launch_recurrence<AT, 1, CHANNEL>(a, num_seqs, stream);
+    }
+    return SHISO_ERR_SHAPE;
+}
+
+SHISO_API int shiso_decay_recurrence(const void* q, const void* k, const void* v, const void* gate, long long q_ld, long long k_ld,
+                                     long long v_ld, long long gate_ld, void* out, long long out_ld, int act_dtype, float* state,
+                                     long long state_stride, const int* q_start, const int* slots, const int* positions,
+                                     const float* decay_logits, long long logits_ld, const float* decay_bias, const float* bonus,
+                                     const float* head_decay, const float* inv_freq, int rotary_dim, float key_scale,
+                                     const float* out_weight, float eps, float out_scale, int num_seqs, int heads, int dim,
+                                     int vdim, cudaStream_t stream) {
+    if (num_seqs <= 0 || heads <= 0) return SHISO_OK;
+    if (dim <= 0 || vdim <= 0 || dim > REC_MAX_DIM || vdim > REC_MAX_DIM || dim * vdim > REC_MAX_STATE) return SHISO_ERR_SHAPE;
+    const bool channel = decay_logits != nullptr;
+    if (channel == (head_decay != nullptr)) return SHISO_ERR_UNSUPPORTED;
+    if (channel && (!decay_bias || !bonus)) return SHISO_ERR_UNSUPPORTED;
+    if (rotary_dim && (channel || !inv_freq || rotary_dim % 2 || rotary_dim > dim)) return SHISO_ERR_UNSUPPORTED;
+    RecurrenceArgs a;
+    a.q = q; a.k = k; a.v = v; a.gate = gate;
+    a.q_ld = q_ld; a.k_ld = k_ld; a.v_ld = v_ld; a.gate_ld = gate_ld; a.out_ld = out_ld;
+    a.out = out; a.state = state; a.state_stride = state_stride;
+    a.q_start = q_start; a.slots = slots; a.positions = positions;
+    a.decay_logits = decay_logits; a.logits_ld = logits_ld; a.decay_bias = decay_bias; a.bonus = bonus;
+    a.head_decay = head_decay; a.inv_freq = inv_freq; a.rotary_dim = rotary_dim; a.key_scale = key_scale;
+    a.out_weight = out_weight; a.eps = eps; a.out_scale = out_scale;
+    a.heads = heads; a.dim = dim; a.vdim = vdim;
+    if (act_dtype == SHISO_F32) return channel ? pick_split<float, true>(a, num_seqs, stream) : pick_split<float, false>(a, num_seqs, stream);
+    if (act_dtype == SHISO_BF16)
+        return channel ? pick_split<__nv_bfloat16, true>(a, num_seqs, stream) : pick_split<__nv_bfloat16, false>(a, num_seqs, stream);
+    return SHISO_ERR_DTYPE;
+}

@@ -328,12 +328,11 @@ class StepBuilder:
             host[lay.want_rows : lay.want_rows + pad_wanted] = self._iota(pad_wanted) if pad_wanted <= len(self._arange) else np.arange(pad_wanted)
         else:
             host[want_at : lay.want_rows + pad_wanted] = 0
-        scratch = np.resize(np.asarray(cache.scratch_pages, dtype=np.int32), width)
         for g in range(self.num_groups):
             at = lay.tables + g * lay.table_elems
             tables = host[at : at + pad_seqs * width].reshape(pad_seqs, width)
             cache.fill_block_tables(requests, g, tables[:real_seqs])
-            tables[real_seqs:] = scratch
+            tables[real_seqs:] = np.resize(np.asarray(cache.scratch_pages_of(g), dtype=np.int32), width)
 
         if self.row_inputs:
             self._fill_extras(host, lay, entries, q_start, pad_tokens)

@@ -262,7 +262,7 @@ class Engine:
         model = Model(plan, env)
         specs = model.tensor_specs()
         if isinstance(tensors_or_dir, str):
-            tensors = load_weights(tensors_or_dir, specs, dtype, device)
+            tensors = load_weights(tensors_or_dir, specs, dtype, device, plan.unused_tensors)
         else:
             tensors = tensors_or_dir
             for name, t in tensors.items():

@@ -818,6 +818,265 @@ def paged_attention(q, heads, kv_heads, head_dim, k_cache, v_cache, block_table,
     return out
 
 
+# --------------------------------------------------------------------------- hashed-pair embedding, copies of the stream
+
+
+def _slot_rows(state: torch.Tensor, name: str, dtype) -> int:
+    """The distance, in elements, between two slots of a per-request state view whose rows are
+    contiguous inside a slot."""
+    if not state.is_cuda or state.dtype != dtype:
+        raise KernelError(f"{name}: expected a {dtype} CUDA tensor, got {state.dtype} on {state.device}")
+    inner = 1
+    for size, stride in zip(reversed(state.shape[1:]), reversed(state.stride()[1:])):
+        if size != 1 and stride != inner:
+            raise KernelError(f"{name}: a slot's values must be contiguous, strides are {state.stride()}")
+        inner *= size
+    return state.stride(0)
+
+
+def embed_hashed_pair(ids, table, pair_table, scale, buckets, mul_prev, mul_cur, step, state, feed_index=None, fed_tokens=None):
+    """``scale * table[id] + pair_table[(previous id * mul_prev + id * mul_cur) mod buckets]``, row
+    ``buckets`` of the pair table for a sequence's first token; float32 rows.  ``state`` (int32
+    ``[slots, 1]``) holds each request's last token + 1 and is brought up to date."""
+    _check(ids, "ids", torch.int32, 1)
+    _check(table, "embedding table", None, 2)
+    _check(pair_table, "pair table", table.dtype, 2)
+    tokens, (vocab, hidden) = ids.shape[0], table.shape
+    if pair_table.shape != (buckets + 1, hidden):
+        raise KernelError(f"a pair table of shape {tuple(pair_table.shape)} for {buckets} buckets and rows of {hidden}")
+    if (feed_index is None) != (fed_tokens is None):
+        raise KernelError("embed: feed_index and fed_tokens come together")
+    stride = _slot_rows(state, "token state", torch.int32)
+    out = torch.empty((tokens, hidden), dtype=torch.float32, device=table.device)
+    status = library().shiso_embed_hashed_pair(
+        _ptr(ids), _ptr(feed_index), _ptr(fed_tokens), _ptr(table), _ptr(pair_table), _code(table), _ptr(step.seq_of_token),
+        _ptr(step.q_start), _ptr(step.start_pos), _ptr(step.state_slots), state.data_ptr(), stride, _ptr(out),
+        tokens, step.num_seqs, hidden, vocab, float(scale), int(buckets), int(mul_prev), int(mul_cur), _stream(),
+    )
+    _done(status, "embed_hashed_pair", 2, shape=(tokens, hidden))
+    return out
+
+
+def _hyper_mix(source, y, mix, write, copies, read, weight, eps, out_dtype, want_sum):
+    single = source.dim() == 2
+    _check(source, "stream", torch.float32, 2 if single else 3)
+    tokens, hidden = source.shape[-2:]
+    if not single and source.shape[0] != copies:
+        raise KernelError(f"{source.shape[0]} copies of the stream where {copies} are expected")
+    lanes = None
+    if y is not None:
+        _check(y, "sublayer output", None, 2)
+        _check(mix, "mixing matrix", torch.float32, 2)
+        _check(write, "write vector", torch.float32, 1)
+        if y.shape != (tokens, hidden) or mix.shape != (copies, copies) or write.shape[0] != copies:
+            raise KernelError("a sublayer output, mixing matrix or write vector of the wrong shape")
+        if not want_sum:
+            lanes = source if not single else torch.empty((copies, tokens, hidden), dtype=torch.float32, device=source.device)
+    normed = summed = None
+    act = out_dtype
+    if read is not None:
+        _check(read, "read vector", torch.float32, 1)
+        _check(weight, "norm weight", torch.float32, 1)
+        if read.shape[0] != copies or weight.shape[0] != hidden:
+            raise KernelError("a read vector or norm weight of the wrong shape")
+        normed = torch.empty((tokens, hidden), dtype=out_dtype, device=source.device)
+    if want_sum:
+        summed = torch.empty((tokens, hidden), dtype=torch.float32, device=source.device)
+    if y is not None:
+        if act is None:
+            act = y.dtype
+        elif y.dtype != act:
+            raise KernelError(f"a sublayer output of {y.dtype} beside normed rows of {act}")
+    status = library().shiso_hyper_mix(
+        _ptr(source), 0 if single else tokens * hidden, _ptr(y), _ptr(mix) if y is not None else 0,
+        _ptr(write) if y is not None else 0, _ptr(lanes), tokens * hidden, _ptr(read), _ptr(weight) if read is not None else 0,
+        float(eps), _ptr(normed), _ptr(summed), _CODES[act if act is not None else torch.float32], tokens, hidden, copies, _stream(),
+    )
+    _done(status, "hyper_mix", shape=(copies, tokens, hidden))
+    return lanes, normed, summed
+
+
+def hyper_mix_read(source, y, mix, write, copies, read, weight, eps, out_dtype):
+    """Copies of the residual stream: writes a sublayer's output into them and reads them for the
+    next sublayer, in one launch.  ``source`` is float32 ``[copies, T, H]``, or ``[T, H]`` standing
+    for every copy.  With ``y``: ``x_r' = sum_s mix[s, r] x_s + write[r] * y`` (in place, or into a
+    new buffer when ``source`` was a single stream).  Returns ``(the copies written or None, rows)``
+    with ``rows = rmsnorm(sum_r read[r] x_r') * weight`` in ``out_dtype``."""
+    lanes, normed, _ = _hyper_mix(source, y, mix, write, copies, read, weight, eps, out_dtype, False)
+    return lanes, normed
+
+
+def hyper_mix_sum(source, y, mix, write):
+    """The sum of the copies after a last write (``y`` may be None): float32 ``[T, H]``."""
+    copies = source.shape[0] if source.dim() == 3 else mix.shape[0]
+    return _hyper_mix(source, y, mix, write, copies, None, None, 0.0, None, True)[2]
+
+
+# --------------------------------------------------------------------------- time mixing, recurrences
+
+
+def token_shift_blend(x, mu, state, step):
+    """``out[c] = x_t + (x_{t-1} - x_t) * mu[c]`` for every row of ``mu``; ``x_{t-1}`` is the row
+    before in the same sequence, the request's kept row (``state``, float32 ``[slots, H]``) for a
+    portion's first token, zeros at position 0.  The kept rows are brought up to date."""
+    _check(x, "x", None, 2)
+    _check(mu, "blend weights", torch.float32, 2)
+    tokens, hidden = x.shape
+    if mu.shape[1] != hidden or state.shape[1:] != (hidden,):
+        raise KernelError(f"blend weights {tuple(mu.shape)} or kept rows {tuple(state.shape)} do not fit rows of {hidden}")
+    stride = _slot_rows(state, "kept rows", torch.float32)
+    out = torch.empty((mu.shape[0], tokens, hidden), dtype=x.dtype, device=x.device)
+    status = library().shiso_token_shift_blend(
+        _ptr(x), _code(x), _ptr(mu), state.data_ptr(), stride, _ptr(step.seq_of_token), _ptr(step.q_start), _ptr(step.start_pos),
+        _ptr(step.state_slots), _ptr(out), tokens, step.num_seqs, hidden, mu.shape[0], _stream(),
+    )
+    _done(status, "token_shift_blend", 2, shape=(mu.shape[0], tokens, hidden))
+    return out
+
+
+_UNARY = {"tanh": 0, "silu": 1}
+
+
+def unary(x, kind, out_dtype):
+    _check(x, "x", None, None)
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    _done(library().shiso_unary(_ptr(x), _code(x), _ptr(out), _code(out), x.numel(), _UNARY[kind], _stream()), f"unary ({kind})",
+          shape=tuple(x.shape))
+    return out
+
+
+def _rows(t, name, dtype, width=None) -> int:
+    """The row stride of a 2-D tensor whose rows are contiguous (a column range of a wider one)."""
+    if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or (dtype is not None and t.dtype != dtype):
+        raise KernelError(f"{name}: expected 2-D CUDA rows of {dtype} with unit column stride, got {t.dtype} {tuple(t.shape)} {t.stride()}")
+    if width is not None and t.shape[1] != width:
+        raise KernelError(f"{name}: rows of {t.shape[1]} where {width} are expected")
+    return t.stride(0)
+
+
+def recurrence_supported(dim: int, vdim: int) -> bool:
+    return bool(library().shiso_decay_recurrence_supported(int(dim), int(vdim)))
+
+
+def decay_recurrence(q, k, v, out, state, step, heads, dim, vdim, eps, *, decay_logits=None, decay_bias=None, bonus=None,
+                     head_decay=None, inv_freq=None, rotary_dim=0, key_scale=1.0, out_weight=None, gate=None, out_scale=1.0):
+    """A matrix state ``S[dim, vdim]`` per head (``state``, float32 ``[slots, heads, dim, vdim]``),
+    walked over each sequence's rows in order.  With ``decay_logits`` (float32 ``[T, heads * dim]``),
+    ``decay_bias`` and ``bonus``: ``w = exp(-exp(logits + bias))``, ``o = (S + diag(bonus) k v^T)^T q``,
+    then ``S = diag(w) S + k v^T``.  With ``head_decay`` (float32 ``[heads]``): q and k rotated by the
+    position (half-split pairs over ``rotary_dim``), k times ``key_scale``, ``S = decay S + k v^T``,
+    then ``o = S^T q``.  ``o`` is brought to unit RMS per head, times ``out_weight``, times
+    ``silu(gate)``, times ``out_scale``, into ``out``.  q, k, v, gate and out may be column ranges."""
+    act = q.dtype
+    tokens = q.shape[0]
+    q_ld, k_ld = _rows(q, "q", act, heads * dim), _rows(k, "k", act, heads * dim)
+    v_ld, out_ld = _rows(v, "v", act, heads * vdim), _rows(out, "out", act, heads * vdim)
+    gate_ld = _rows(gate, "gate", act, heads * vdim) if gate is not None else 0
+    if state.shape[1:] != (heads, dim, vdim):
+        raise KernelError(f"a state of shape {tuple(state.shape)} for {heads} heads of {dim} x {vdim}")
+    stride = _slot_rows(state, "recurrent state", torch.float32)
+    logits_ld = 0
+    if decay_logits is not None:
+        logits_ld = _rows(decay_logits, "decay logits", torch.float32, heads * dim)
+        _check(decay_bias, "decay bias", torch.float32, 1)
+        _check(bonus, "bonus", torch.float32, 2)
+        if decay_bias.shape[0] != heads * dim or bonus.shape != (heads, dim):
+            raise KernelError("a decay bias or bonus of the wrong shape")
+    if head_decay is not None:
+        _check(head_decay, "head decay", torch.float32, 1)
+        if head_decay.shape[0] != heads:
+            raise KernelError(f"{head_decay.shape[0]} decays for {heads} heads")
+    if rotary_dim:
+        _check(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.shape[0] != rotary_dim // 2:
+            raise KernelError(f"inv_freq has {inv_freq.shape[0]} entries for a rotation over {rotary_dim}")
+    if out_weight is not None:
+        _check(out_weight, "output weight", torch.float32, 1)
+        if out_weight.shape[0] != heads * vdim:
+            raise KernelError(f"an output weight of {out_weight.shape[0]} for {heads} heads of {vdim}")
+    status = library().shiso_decay_recurrence(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), gate.data_ptr() if gate is not None else 0, q_ld, k_ld, v_ld, gate_ld,
+        out.data_ptr(), out_ld, _CODES[act], state.data_ptr(), stride, _ptr(step.q_start), _ptr(step.state_slots),
+        _ptr(step.positions), _ptr(decay_logits), logits_ld, _ptr(decay_bias), _ptr(bonus), _ptr(head_decay),
+        _ptr(inv_freq) if rotary_dim else 0, int(rotary_dim), float(key_scale), _ptr(out_weight), float(eps), float(out_scale),
+        step.num_seqs, heads, dim, vdim, _stream(),
+    )
+    _done(status, "decay_recurrence", shape=(tokens, heads, dim, vdim))
+    return out
+
+
+# --------------------------------------------------------------------------- windowed attention with pooled blocks
+
+
+def _paged(cache, name, dtype, page_size):
+    _check(cache, name, dtype, 4)
+    if cache.shape[1] != page_size:
+        raise KernelError(f"{name} of shape {tuple(cache.shape)} does not have pages of {page_size}")
+
+
+def store_kv(k, v, kv_heads, dim, vdim, step, k_cache, v_cache, block_table, page_size):
+    """A step's keys and values, as they are, into the paged caches (``k`` and ``v`` may be column ranges)."""
+    act = k.dtype
+    k_ld, v_ld = _rows(k, "k", act, kv_heads * dim), _rows(v, "v", act, kv_heads * vdim)
+    _paged(k_cache, "k cache", act, page_size)
+    _paged(v_cache, "v cache", act, page_size)
+    if k_cache.shape[2:] != (kv_heads, dim) or v_cache.shape[2:] != (kv_heads, vdim):
+        raise KernelError(f"caches of shape {tuple(k_cache.shape)} / {tuple(v_cache.shape)} for {kv_heads} heads of {dim} / {vdim}")
+    _check(block_table, "block table", torch.int32, 2)
+    status = library().shiso_store_kv(
+        k.data_ptr(), k_ld, v.data_ptr(), v_ld, _CODES[act], _ptr(step.positions), _ptr(step.seq_of_token), _ptr(block_table),
+        block_table.shape[1], _ptr(k_cache), _ptr(v_cache), k.shape[0], kv_heads, dim, vdim, page_size, _stream(),
+    )
+    _done(status, "store_kv", shape=(k.shape[0], kv_heads, dim + vdim))
+
+
+def pool_kv(k_cache, v_cache, block_table, pooled_k, pooled_v, pooled_table, page_size, pool, step):
+    """For every row of the step whose position ends a block of ``pool`` positions: the means of
+    the block's cached keys and values (float32) as row ``position // pool`` of the pooled caches."""
+    _paged(k_cache, "k cache", None, page_size)
+    _paged(v_cache, "v cache", k_cache.dtype, page_size)
+    _paged(pooled_k, "pooled k cache", torch.float32, page_size)
+    _paged(pooled_v, "pooled v cache", torch.float32, page_size)
+    if pooled_k.shape[2:] != k_cache.shape[2:] or pooled_v.shape[2:] != v_cache.shape[2:]:
+        raise KernelError("pooled caches whose heads differ from the caches they summarise")
+    _check(block_table, "block table", torch.int32, 2)
+    _check(pooled_table, "pooled block table", torch.int32, 2)
+    if pooled_table.shape != block_table.shape:
+        raise KernelError("the two block tables of a step have one shape")
+    kv_heads, dim, vdim = k_cache.shape[2], k_cache.shape[3], v_cache.shape[3]
+    status = library().shiso_pool_kv(
+        _ptr(k_cache), _ptr(v_cache), _code(k_cache), _ptr(block_table), _ptr(pooled_k), _ptr(pooled_v), _ptr(pooled_table),
+        block_table.shape[1], _ptr(step.positions), _ptr(step.seq_of_token), step.num_tokens, kv_heads, dim, vdim, page_size,
+        int(pool), _stream(),
+    )
+    _done(status, "pool_kv", shape=(step.num_tokens, kv_heads, dim + vdim))
+
+
+def pooled_window_attention(q, heads, k_cache, v_cache, block_table, pooled_k, pooled_v, pooled_table, page_size, scale,
+                            window, pool, step, out, out_scale=1.0):
+    """Softmax attention of every row over the last ``window`` positions of its sequence and, in
+    the same softmax, the pooled key and value of every block of ``pool`` positions that lies
+    wholly behind the window; ``out`` (a column range, like ``q``) gets the result times ``out_scale``."""
+    act = q.dtype
+    kv_heads, dim, vdim = k_cache.shape[2], k_cache.shape[3], v_cache.shape[3]
+    q_ld, out_ld = _rows(q, "q", act, heads * dim), _rows(out, "out", act, heads * vdim)
+    _paged(k_cache, "k cache", act, page_size)
+    _paged(v_cache, "v cache", act, page_size)
+    _paged(pooled_k, "pooled k cache", torch.float32, page_size)
+    _paged(pooled_v, "pooled v cache", torch.float32, page_size)
+    _check(block_table, "block table", torch.int32, 2)
+    _check(pooled_table, "pooled block table", torch.int32, 2)
+    if pooled_table.shape != block_table.shape:
+        raise KernelError("the two block tables of a step have one shape")
+    status = library().shiso_pooled_window_attention(
+        q.data_ptr(), q_ld, _CODES[act], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(pooled_k), _ptr(pooled_v),
+        _ptr(pooled_table), block_table.shape[1], _ptr(step.positions), _ptr(step.seq_of_token), out.data_ptr(), out_ld,
+        q.shape[0], heads, kv_heads, dim, vdim, page_size, float(scale), int(window), int(pool), float(out_scale), _stream(),
+    )
+    _done(status, "pooled_window_attention", shape=(q.shape[0], heads, dim))
+    return out
+
+
 # --------------------------------------------------------------------------- sampling
 
 

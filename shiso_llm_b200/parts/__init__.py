@@ -7,6 +7,7 @@ from .base import (
     Part, PositionEncoding, Registry, Stream,
 )
 from . import norm, position, attention, short_conv, feed_forward, block, embedding  # register built-ins
+from . import hyper, wkv, retention, pooled_attention, parallel  # noqa: F401  (more built-ins)
 from .model import Model
 
 __all__ = [

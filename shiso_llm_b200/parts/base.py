@@ -48,13 +48,19 @@ class PagedKV:
     """Keys and values of every position, in pages.  ``window`` = how many of the most
     recent positions are ever read again (None: all of them).  Values may have another width
     than keys (``v_head_dim``; None: the same), and the entry may ask for an element type of
-    its own (``dtype``; None: the engine's compute type)."""
+    its own (``dtype``; None: the engine's compute type).  ``every`` > 1 asks for one row per
+    complete run of that many positions instead of one per position (summaries of blocks of
+    tokens): a request of ``n`` positions then holds ``n // every`` rows.
+
+    A mixer that needs more than one cache returns a tuple of needs from ``cache_spec`` and
+    is handed a tuple of views in the same order."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
     v_head_dim: Optional[int] = None
     dtype: Optional[torch.dtype] = None
+    every: int = 1
 
     @property
     def value_dim(self) -> int:
@@ -154,6 +160,11 @@ class FeedForward(Part):
 
 
 class Embedding(Part):
+    def cache_spec(self):
+        """``FixedState`` when the embedding keeps something per request (it is then handed the
+        view as ``forward(step, cache)``), else None."""
+        return None
+
     def forward(self, step) -> torch.Tensor:
         """Float32 residual rows ``[T, hidden]`` for ``step.token_ids``."""
         raise NotImplementedError
@@ -254,6 +265,37 @@ class Stream:
         self.residual = residual
         self.pending: Optional[torch.Tensor] = None
         self.observer = observer  # a diagnostic: called with the stream after every ``add``
+        # A block arrangement that keeps several copies of the stream (hyper-connections) holds
+        # them here, float32 ``[copies, T, hidden]``; None while there is one stream, and then
+        # ``residual`` stands for every copy.  ``lane_update = (y, mix, out)`` is a sublayer
+        # output not yet written into the copies: the next read writes it in the same kernel.
+        self.lanes: Optional[torch.Tensor] = None
+        self.lane_update = None
+
+    def lane_values(self) -> Optional[torch.Tensor]:
+        """The copies with the waiting update applied, computed on the side (a diagnostic);
+        None while there is one stream."""
+        if self.lanes is None and self.lane_update is None:
+            return None
+        if self.lanes is not None:
+            lanes = self.lanes
+        else:
+            lanes = self.residual.unsqueeze(0).expand(self.lane_update[1].shape[0], -1, -1)
+        if self.lane_update is None:
+            return lanes.clone()
+        y, mix, out = self.lane_update
+        return torch.einsum("sr,std->rtd", mix.to(lanes.dtype), lanes) + out.to(lanes.dtype)[:, None, None] * y.to(lanes.dtype)[None]
+
+    def merge_lanes(self, ops) -> None:
+        """Ends the copies: ``residual`` becomes their sum (with the waiting update applied)."""
+        if self.lanes is None and self.lane_update is None:
+            return
+        if self.lane_update is None:
+            self.residual = ops.hyper_mix_sum(self.lanes, None, None, None)
+        else:
+            y, mix, out = self.lane_update
+            self.residual = ops.hyper_mix_sum(self.lanes if self.lanes is not None else self.residual, y, mix, out)
+        self.lanes = self.lane_update = None
 
     def normed(self, norm: Norm, deferred: bool = False):
         """The normed rows; with ``deferred`` a ``DeferredNorm`` that computes them when (and how)

@@ -20,6 +20,9 @@ from .plan import ModelPlan
 def stream_value(stream: Stream) -> torch.Tensor:
     """The residual stream as float32 rows, with the block output that is still waiting to be
     added, without touching the stream: a product that has not run is run on the side."""
+    lanes = stream.lane_values()
+    if lanes is not None:
+        return lanes.sum(0)
     x = stream.residual
     waiting = stream.pending
     if waiting is None:
@@ -81,13 +84,16 @@ class Model:
     # ------------------------------------------------------------------ cache needs
 
     def cache_needs(self) -> list:
-        """Per run entry: the cache its mixer needs, or None (also for a borrowing entry)."""
+        """Per run entry: the cache its mixer needs (one need, a tuple of needs, or None - also
+        for a borrowing entry); behind the run entries, the embedding's need if it has one."""
         needs = []
         for entry in self.plan.order:
             if entry.cache_of is not None:
                 needs.append(None)
             else:
                 needs.append(self.blocks[entry.layer].mixer_part().cache_spec())
+        if self.embedding.cache_spec() is not None:
+            needs.append(self.embedding.cache_spec())
         return needs
 
     # ------------------------------------------------------------------ one step
@@ -103,7 +109,10 @@ class Model:
         so a step with a hook is never captured."""
         if not self.bound:
             raise RuntimeError("the model has no weights yet: load or bind them first")
-        stream = Stream(self.embedding.forward(step), add_hook)
+        if self.embedding.cache_spec() is not None:
+            stream = Stream(self.embedding.forward(step, cache.view(len(self.plan.order))), add_hook)
+        else:
+            stream = Stream(self.embedding.forward(step), add_hook)
         if layer_hook is not None:
             layer_hook(-1, stream)
         for pos, entry in enumerate(self.plan.order):
@@ -116,6 +125,7 @@ class Model:
                 layer_hook(pos, stream)
         if step.num_wanted == 0:
             return None
+        stream.merge_lanes(self.env.ops)
         if getattr(step, "wants_every_row", False):
             # every row in order (a decode step): the norm that closes the last block is the final norm
             # (handed over unevaluated to a head that says it takes that: its product may apply the row scale itself)

@@ -4,11 +4,17 @@ The weight multiplies directly, not as ``1 + w`` (kernels/cuda/generic/norm.cuh:
 ``add_apply`` is the fused residual-add + norm that closes every block
 (norm.cuh:105-165; crates/shiso-engine/src/layers.rs:2476-2498): the stored sum is
 what is normalised.
+
+``offset`` (default 0) is added to the stored weight once, when it is bound: a checkpoint
+that keeps its norm weights around zero and applies ``1 + w`` asks for ``offset = 1`` and
+every kernel runs unchanged.
 """
 
 from __future__ import annotations
 
-from ..weights.spec import ONES, VECTOR, TensorSpec
+import torch
+
+from ..weights.spec import NORMAL, ONES, VECTOR, TensorSpec
 from .base import NORMS, Norm
 
 
@@ -19,13 +25,18 @@ class RMSNorm(Norm):
         self.tensor_name = spec.params["tensor"]
         self.size = int(spec.params["size"])
         self.eps = float(spec.params["eps"])
+        self.offset = float(spec.params.get("offset", 0.0))
         self.weight = None
 
     def tensor_specs(self):
+        if self.offset != 0.0:  # stored around zero
+            return [TensorSpec(self.tensor_name, (self.size,), VECTOR, NORMAL, init_std=0.1)]
         return [TensorSpec(self.tensor_name, (self.size,), VECTOR, ONES)]
 
     def bind(self, tensors):
         self.weight = tensors[self.tensor_name]
+        if self.offset != 0.0:
+            self.weight = (self.weight.to(torch.float32) + self.offset).contiguous()
 
     def rms_params(self):
         """``(weight, eps)``: what a kernel that normalises inside a product needs."""

@@ -86,6 +86,9 @@ class ModelPlan:
     # crates/shiso-engine/src/attn.rs:244-284).  A caller gives them per entry
     # (``StepEntry.extras``); a row for which none is given gets its position.
     row_inputs: tuple[str, ...] = ()
+    # Tensors a checkpoint of this model may hold that no part reads (norms and the like of a
+    # sublayer the configuration leaves out): the loader passes over them instead of refusing.
+    unused_tensors: tuple[str, ...] = ()
 
     def __post_init__(self):
         if self.portion_multiple < 1:

@@ -64,6 +64,12 @@ def target_dtype(spec: TensorSpec, stored: torch.dtype, compute_dtype: torch.dty
     return torch.bfloat16
 
 
+def shape_fits(stored: tuple, wanted: tuple) -> bool:
+    """Whether a stored shape is the wanted one; a wanted extent of -1 takes any (a size that
+    only the file gives, such as the rank of a low-rank pair)."""
+    return len(stored) == len(wanted) and all(w == -1 or s == w for s, w in zip(stored, wanted))
+
+
 def weight_files(model_dir: str) -> list[str]:
     return sorted(glob.glob(os.path.join(model_dir, "*.safetensors")))
 
@@ -73,9 +79,12 @@ def load_weights(
     specs: Iterable[TensorSpec],
     compute_dtype: torch.dtype,
     device,
+    unused: Iterable[str] = (),
 ) -> dict[str, torch.Tensor]:
-    """Loads exactly the tensors ``specs`` names; anything else is an error."""
+    """Loads exactly the tensors ``specs`` names; anything else is an error, except the names
+    in ``unused``, which may be present and are passed over."""
     specs = list(specs)
+    unused = set(unused)
     paths = weight_files(model_dir)
     if not paths:
         raise WeightError(model_dir, [s.name for s in specs], [], [], [], ["no *.safetensors file in the folder"])
@@ -104,13 +113,13 @@ def load_weights(
         other.append("the model asks twice for: " + ", ".join(sorted(set(twice))))
 
     missing = sorted(n for n in wanted if n not in home)
-    unexpected = sorted(n for n in home if n not in wanted)
+    unexpected = sorted(n for n in home if n not in wanted and n not in unused)
     wrong_shape, wrong_dtype = [], []
     for name, spec in wanted.items():
         if name not in home:
             continue
         entry = home[name].entries[name]
-        if entry.shape != tuple(spec.shape) and entry.shape not in spec.alt_shapes:
+        if not shape_fits(entry.shape, tuple(spec.shape)) and entry.shape not in spec.alt_shapes:
             wrong_shape.append((name, spec.shape, entry.shape))
         if spec.role == INDEX:
             if entry.dtype not in _INTS:
@@ -126,7 +135,8 @@ def load_weights(
     for name, spec in wanted.items():
         view = home[name].tensor(name)
         dtype = target_dtype(spec, view.dtype, compute_dtype)
-        tensor = view.to(device=device, dtype=dtype, copy=True).reshape(spec.shape).contiguous()
+        shape = spec.shape if -1 not in spec.shape else view.shape
+        tensor = view.to(device=device, dtype=dtype, copy=True).reshape(shape).contiguous()
         out[name] = tensor
     for f in files:
         f.close()

@@ -18,7 +18,7 @@ from typing import Iterable, Mapping
 import torch
 
 from .safetensors_io import write_safetensors
-from .spec import INDEX, NORMAL, ONES, VECTOR, ZEROS, TensorSpec
+from .spec import IDENTITY, INDEX, NORMAL, ONES, VECTOR, ZEROS, TensorSpec
 
 _STORAGE = {"bfloat16": torch.bfloat16, "float32": torch.float32, "float16": torch.float16}
 
@@ -39,10 +39,13 @@ def random_tensors(
     for spec in sorted(specs, key=lambda s: s.name):
         if spec.role == INDEX:
             raise ValueError(f"{spec.name}: integer tables have no random initialisation")
+        if -1 in spec.shape:
+            raise ValueError(f"{spec.name}: the shape {list(spec.shape)} leaves a size to the file; random weights need it named")
         if spec.init == NORMAL:
-            t = torch.randn(spec.shape, generator=gen, dtype=torch.float32) * std
-        elif spec.init == ONES:
-            t = torch.ones(spec.shape, dtype=torch.float32)
+            t = torch.randn(spec.shape, generator=gen, dtype=torch.float32) * (std if spec.init_std is None else spec.init_std)
+            t = t + spec.init_mean
+        elif spec.init in (ONES, IDENTITY):
+            t = torch.ones(spec.shape, dtype=torch.float32) if spec.init == ONES else torch.eye(spec.shape[0], spec.shape[1])
             if norm_jitter:
                 t = t + norm_jitter * torch.randn(spec.shape, generator=gen, dtype=torch.float32)
         elif spec.init == ZEROS:
@@ -71,9 +74,12 @@ def random_device_tensors(specs: Iterable[TensorSpec], seed: int, compute_dtype,
     for spec in sorted(specs, key=lambda s: s.name):
         dtype = torch.float32 if spec.role == VECTOR else compute_dtype
         if spec.init == NORMAL:
-            t = torch.empty(spec.shape, dtype=torch.float32, device=device).normal_(0.0, std, generator=gen)
+            t = torch.empty(spec.shape, dtype=torch.float32, device=device).normal_(
+                spec.init_mean, std if spec.init_std is None else spec.init_std, generator=gen)
         elif spec.init == ONES:
             t = torch.ones(spec.shape, dtype=torch.float32, device=device)
+        elif spec.init == IDENTITY:
+            t = torch.eye(spec.shape[0], spec.shape[1], dtype=torch.float32, device=device)
         else:
             t = torch.zeros(spec.shape, dtype=torch.float32, device=device)
         out[spec.name] = t.to(dtype)

@@ -11,6 +11,7 @@ INDEX = "index"  # integer tables: kept as int32
 NORMAL = "normal"
 ONES = "ones"
 ZEROS = "zeros"
+IDENTITY = "identity"  # a square matrix: the unit matrix (jittered like ONES when a test asks for it)
 
 
 @dataclass(frozen=True)
@@ -26,3 +27,6 @@ class TensorSpec:
     role: str = MATRIX
     init: str = NORMAL
     alt_shapes: tuple[tuple[int, ...], ...] = ()
+    # Random weights: NORMAL draws around ``init_mean`` with ``init_std`` (None: the caller's std).
+    init_mean: float = 0.0
+    init_std: float | None = None

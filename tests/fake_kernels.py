@@ -232,3 +232,193 @@ def argmax(logits, out=None, status_out=None):
         return picks
     out.copy_(picks)
     return out
+
+
+# --------------------------------------------------------------------------- hashed-pair embedding, stream copies
+
+
+def _step_ids(ids, feed_index, fed_tokens):
+    ids = ids.long()
+    if feed_index is not None:
+        fed = fed_tokens.long()[feed_index.long().clamp(min=0)]
+        ids = torch.where(feed_index.long() >= 0, fed, ids)
+    return ids
+
+
+def embed_hashed_pair(ids, table, pair_table, scale, buckets, mul_prev, mul_cur, step, state, feed_index=None, fed_tokens=None):
+    """``scale * table[id] + pair_table[hash(previous id, id)]``; a sequence's first token takes
+    row ``buckets``.  ``state[slot, 0]`` holds a request's last token + 1."""
+    ids = _step_ids(ids, feed_index, fed_tokens).tolist()
+    q_start, slots, starts = step.q_start.tolist(), step.state_slots.tolist(), step.start_pos.tolist()
+    out = torch.zeros(len(ids), table.shape[1], dtype=F64)
+    for s in range(step.num_seqs):
+        a, e = q_start[s], q_start[s + 1]
+        if e <= a:
+            continue
+        for t in range(a, e):
+            if t > a:
+                prev = ids[t - 1]
+            elif starts[s] == 0:
+                prev = None
+            else:
+                prev = int(state[slots[s], 0]) - 1
+            row = buckets if prev is None else (prev * mul_prev + ids[t] * mul_cur) % buckets
+            out[t] = table[ids[t]].to(F64) * scale + pair_table[row].to(F64)
+        state[slots[s], 0] = ids[e - 1] + 1
+    return out.to(torch.float32)
+
+
+def _mixed_lanes(source, y, mix, write, copies):
+    lanes = source.to(F64) if source.dim() == 3 else source.to(F64).unsqueeze(0).expand(copies, -1, -1)
+    if y is None:
+        return lanes
+    return torch.einsum("sr,std->rtd", mix.to(F64), lanes) + write.to(F64)[:, None, None] * y.to(F64)[None]
+
+
+def hyper_mix_read(source, y, mix, write, copies, read, weight, eps, out_dtype):
+    new = _mixed_lanes(source, y, mix, write, copies)
+    lanes = None
+    if y is not None:
+        if source.dim() == 3:
+            source.copy_(new.to(source.dtype))
+            lanes = source
+        else:
+            lanes = new.to(torch.float32).contiguous()
+        new = lanes.to(F64)  # what the next sublayer reads is what was stored
+    u = torch.einsum("s,std->td", read.to(F64), new)
+    x = u / torch.sqrt((u * u).mean(-1, keepdim=True) + eps) * weight.to(F64)
+    return lanes, x.to(out_dtype)
+
+
+def hyper_mix_sum(source, y, mix, write):
+    copies = source.shape[0] if source.dim() == 3 else mix.shape[0]
+    return _mixed_lanes(source, y, mix, write, copies).sum(0).to(torch.float32)
+
+
+# --------------------------------------------------------------------------- time mixing, recurrences
+
+
+def token_shift_blend(x, mu, state, step):
+    T, H = x.shape
+    x64 = x.to(F64)
+    prev = torch.zeros_like(x64)
+    q_start, slots = step.q_start.tolist(), step.state_slots.tolist()
+    for s in range(step.num_seqs):
+        a, e = q_start[s], q_start[s + 1]
+        if e <= a:
+            continue
+        prev[a] = state[slots[s]].to(F64)
+        prev[a + 1 : e] = x64[a : e - 1]
+        state[slots[s]] = x64[e - 1].to(state.dtype)
+    return (x64[None] + (prev - x64)[None] * mu.to(F64)[:, None, :]).to(x.dtype)
+
+
+def unary(x, kind, out_dtype):
+    x64 = x.to(F64)
+    if kind == "tanh":
+        return torch.tanh(x64).to(out_dtype)
+    if kind == "silu":
+        return (x64 / (1.0 + torch.exp(-x64))).to(out_dtype)
+    raise ValueError(kind)
+
+
+def decay_recurrence(q, k, v, out, state, step, heads, dim, vdim, eps, *, decay_logits=None, decay_bias=None, bonus=None,
+                     head_decay=None, inv_freq=None, rotary_dim=0, key_scale=1.0, out_weight=None, gate=None, out_scale=1.0):
+    """Per head ``S[dim, vdim]``.  With ``decay_logits``: ``w = exp(-exp(logits + bias))`` per key
+    channel, ``o = (S + diag(bonus) k v^T)^T q`` and then ``S = diag(w) S + k v^T``.  With
+    ``head_decay``: ``S = decay S + k v^T`` and then ``o = S^T q``; q and k are rotated (half-split
+    pairs of the first ``rotary_dim`` channels) and k multiplied by ``key_scale`` first.  ``o`` is
+    brought to unit RMS per head, times ``out_weight``, times ``silu(gate)``, times ``out_scale``."""
+    T = q.shape[0]
+    q64 = q.to(F64).reshape(T, heads, dim).clone()
+    k64 = k.to(F64).reshape(T, heads, dim).clone()
+    v64 = v.to(F64).reshape(T, heads, vdim)
+    if rotary_dim:
+        half = rotary_dim // 2
+        angle = step.positions.to(F64)[:, None] * inv_freq.to(F64)[None, :]
+        cos, sin = torch.cos(angle)[:, None, :], torch.sin(angle)[:, None, :]
+        for x in (q64, k64):
+            a, b = x[..., :half].clone(), x[..., half:rotary_dim].clone()
+            x[..., :half] = a * cos - b * sin
+            x[..., half:rotary_dim] = b * cos + a * sin
+    k64 = k64 * key_scale
+    if decay_logits is not None:
+        w = torch.exp(-torch.exp(decay_logits.to(F64) + decay_bias.to(F64))).reshape(T, heads, dim)
+    o = torch.zeros(T, heads, vdim, dtype=F64)
+    q_start, slots = step.q_start.tolist(), step.state_slots.tolist()
+    for s in range(step.num_seqs):
+        S = state[slots[s]].to(F64)
+        for t in range(q_start[s], q_start[s + 1]):
+            kv = k64[t][:, :, None] * v64[t][:, None, :]
+            if decay_logits is not None:
+                o[t] = torch.einsum("hi,hij->hj", q64[t], S + bonus.to(F64)[:, :, None] * kv)
+                S = w[t][:, :, None] * S + kv
+            else:
+                S = head_decay.to(F64)[:, None, None] * S + kv
+                o[t] = torch.einsum("hi,hij->hj", q64[t], S)
+        if q_start[s + 1] > q_start[s]:
+            state[slots[s]] = S.to(state.dtype)
+    o = (o / torch.sqrt((o * o).mean(-1, keepdim=True) + eps)).reshape(T, heads * vdim)
+    if out_weight is not None:
+        o = o * out_weight.to(F64)
+    if gate is not None:
+        g = gate.to(F64)
+        o = o * (g / (1.0 + torch.exp(-g)))
+    out.copy_((o * out_scale).to(out.dtype))
+    return out
+
+
+# --------------------------------------------------------------------------- windowed attention with pooled blocks
+
+
+def store_kv(k, v, kv_heads, dim, vdim, step, k_cache, v_cache, block_table, page_size):
+    rows = _cache_rows(block_table, step.seq_of_token, step.positions, page_size)
+    T = k.shape[0]
+    k_cache.view(-1, kv_heads, dim)[rows] = k.reshape(T, kv_heads, dim).to(k_cache.dtype)
+    v_cache.view(-1, kv_heads, vdim)[rows] = v.reshape(T, kv_heads, vdim).to(v_cache.dtype)
+
+
+def pool_kv(k_cache, v_cache, block_table, pooled_k, pooled_v, pooled_table, page_size, pool, step):
+    """For every row whose position ends a block of ``pool`` positions: the means of the block's
+    cached keys and values, stored as row ``position // pool`` of the pooled caches."""
+    kf, vf = k_cache.flatten(0, 1), v_cache.flatten(0, 1)
+    pkf, pvf = pooled_k.flatten(0, 1), pooled_v.flatten(0, 1)
+    seq, pos = step.seq_of_token.tolist(), step.positions.tolist()
+    for t in range(len(pos)):
+        if (pos[t] + 1) % pool:
+            continue
+        ps = torch.arange(pos[t] + 1 - pool, pos[t] + 1)
+        rows = block_table[seq[t]].long()[ps // page_size] * page_size + ps % page_size
+        b = pos[t] // pool
+        at = int(pooled_table[seq[t], b // page_size]) * page_size + b % page_size
+        pkf[at] = kf[rows].to(F64).mean(0).to(pooled_k.dtype)
+        pvf[at] = vf[rows].to(F64).mean(0).to(pooled_v.dtype)
+
+
+def pooled_window_attention(q, heads, k_cache, v_cache, block_table, pooled_k, pooled_v, pooled_table, page_size, scale,
+                            window, pool, step, out, out_scale=1.0):
+    T = q.shape[0]
+    kv_heads, d, dv = k_cache.shape[2], k_cache.shape[3], v_cache.shape[3]
+    group = heads // kv_heads
+    q64 = q.to(F64).reshape(T, heads, d)
+    kf, vf = k_cache.flatten(0, 1), v_cache.flatten(0, 1)
+    pkf, pvf = pooled_k.flatten(0, 1), pooled_v.flatten(0, 1)
+    res = torch.zeros(T, heads, dv, dtype=F64)
+    seq, pos = step.seq_of_token.tolist(), step.positions.tolist()
+    for t in range(T):
+        i = pos[t]
+        ps = torch.arange(max(0, i - window + 1), i + 1)
+        rows = block_table[seq[t]].long()[ps // page_size] * page_size + ps % page_size
+        keys, values = kf[rows].to(F64), vf[rows].to(F64)
+        blocks = max(0, (i - window + 1) // pool)
+        if blocks:
+            bs = torch.arange(blocks)
+            prow = pooled_table[seq[t]].long()[bs // page_size] * page_size + bs % page_size
+            keys = torch.cat([pkf[prow].to(F64), keys])
+            values = torch.cat([pvf[prow].to(F64), values])
+        for h in range(heads):
+            g = h // group
+            p = torch.softmax((keys[:, g] @ q64[t, h]) * scale, dim=0)
+            res[t, h] = p @ values[:, g]
+    out.copy_((res.reshape(T, heads * dv) * out_scale).to(out.dtype))
+    return out
