@@ -20,6 +20,11 @@ The model's weights (1.8 GB) are read every step and exceed the 126 MB L2, so co
 steps do not reuse cached inputs.  ``points`` also carries two serving workloads after the
 reference's own benchmark scenarios (350M shape: 64 concurrent requests; 2.6B shape: a long prompt in portions
 beside 32 decoding streams), unless ``--points`` leaves them out.
+
+``--designs PRESET[,PRESET...]`` leaves the headline aside and prints, for each named preset
+(say ``filulix-1b,lfm2-1.2b``: two designs at one width, depth and feed-forward size), the time
+of one prompt step and of a decode step at ``--batch`` and ``--prompt-len``, each with the
+table of its launches - the figures that set one design's kernels beside the other's.
 """
 
 from __future__ import annotations
@@ -272,6 +277,99 @@ def run_workload(workload, preset, config, plan, full_layers) -> dict:
             "value": results["mixed"]["prompt_tok_s"], **results, "graph_replays": graph_replays(llm.engine)}
 
 
+def compare_designs(args) -> dict:
+    """Prompt and decode throughput of several presets side by side (random bfloat16 weights made
+    on the device), each with the per-launch table of one prompt step and of the decode steps:
+    what ``--designs`` prints.  A prompt step is ``--prompt-len`` tokens of one request; decode
+    steps run ``--batch`` requests at that context, replayed from a captured graph, timed with
+    CUDA events around ``--steps`` steps after ``--warmup``.  Every step's inputs are other
+    tokens than the last one's, and a step reads every weight (more than L2 holds) once."""
+    import torch
+
+    from shiso_llm_b200.cli import preset_path
+    from shiso_llm_b200.config import plan_from_document
+    from shiso_llm_b200.engine import Engine, EngineOptions, StepEntry
+    from shiso_llm_b200.kernels import ops
+    from shiso_llm_b200.parts import BuildEnv, Model
+    from shiso_llm_b200.weights import random_device_tensors
+
+    device = torch.device("cuda:0")
+    ops.require()
+    peak, peak_source = peaks()
+    tokens, batch = args.prompt_len, args.batch
+    gen = torch.Generator().manual_seed(99)
+    designs = {}
+    for name in [n.strip() for n in args.designs.split(",") if n.strip()]:
+        with open(preset_path(name)) as f:
+            _, config, plan = plan_from_document(json.load(f))
+        probe = Model(plan, BuildEnv(dtype=torch.bfloat16, device=device, ops=ops))
+        specs = probe.tensor_specs()
+        del probe
+        tensors = random_device_tensors(specs, 0, torch.bfloat16, device)
+        parameters = sum(t.numel() for t in tensors.values())
+        ctx = -(-(tokens + args.steps + args.warmup + 80) // 16) * 16
+        engine = Engine.from_plan(plan, tensors, EngineOptions(
+            dtype="bfloat16", ctx=ctx, page_size=16, kv_cache_tokens=(batch + 1) * ctx, max_num_seqs=batch + 1,
+            max_num_batched_tokens=tokens, cuda_graphs=not args.no_cuda_graphs))
+
+        def prompt():
+            return torch.randint(0, plan.vocab_size, (tokens,), generator=gen).tolist()
+
+        times = []
+        for i in range(3 + 5):
+            torch.cuda.synchronize()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            engine.step([StepEntry(("p", i), prompt(), [tokens - 1])])
+            end.record()
+            torch.cuda.synchronize()
+            engine.finish(("p", i))
+            if i >= 3:
+                times.append(start.elapsed_time(end))
+        prefill_ms = statistics.median(times)
+        requests = [("d", i) for i in range(batch)]
+        for r in requests:
+            engine.step([StepEntry(r, prompt(), [tokens - 1])])
+        entries = [StepEntry(r, [int(torch.randint(0, plan.vocab_size, (1,), generator=gen))], [0]) for r in requests]
+        for _ in range(args.warmup):
+            ops.argmax(engine.step(entries))
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(args.steps):
+            ops.argmax(engine.step(entries))
+        end.record()
+        torch.cuda.synchronize()
+        ops.check_kernel_status()
+        decode_ms = start.elapsed_time(end) / args.steps
+        profiler = engine.enable_launch_profile()
+        engine.step([StepEntry(("p", "profiled"), prompt(), [tokens - 1])])
+        engine.finish(("p", "profiled"))
+        for _ in range(3):
+            engine.step(entries)
+        engine.disable_launch_profile()
+        report = profiler.report()
+        for r in requests:
+            engine.finish(r)
+
+        def top(kind):
+            return [{"kernel": r["kernel"], "shape": r["shape"], "launches": r["launches_per_step"], "us": round(r["us_per_step"], 1)}
+                    for r in report[kind]["rows"][:14]]
+
+        designs[name] = {
+            "parameters": parameters,
+            "prefill": {"tokens": tokens, "ms": prefill_ms, "tok_s": tokens / (prefill_ms / 1e3), "spread": max(times) / min(times) - 1.0},
+            "decode": {"batch": batch, "context": tokens, "ms_per_step": decode_ms, "tok_s": batch / (decode_ms / 1e3)},
+            "prompt_step_launches": top("prompt"), "decode_step_launches": top("decode"),
+            "prompt_step_device_us": report["prompt"]["device_us_per_step"],
+            "decode_step_device_us": report["decode"]["device_us_per_step"],
+        }
+        del engine, tensors
+        torch.cuda.empty_cache()
+    return {"designs": designs, "peaks": peak, "peak_source": peak_source, "dtype": "bf16", "data": "synthetic",
+            "steps": args.steps, "warmup": args.warmup}
+
+
 def main() -> int:
     global PROMPT_LEN
     parser = argparse.ArgumentParser()
@@ -289,6 +387,9 @@ def main() -> int:
     parser.add_argument("--reps", type=int, default=7, help="timed repetitions of the K-step block (after one that is discarded)")
     parser.add_argument("--no-cuda-graphs", action="store_true")
     parser.add_argument("--skip-prefill", action="store_true")
+    parser.add_argument("--designs", default=None, metavar="PRESET[,PRESET...]",
+                        help="instead of the headline: prompt and decode throughput of these presets side by side, with "
+                             "each one's per-launch table (for instance filulix-1b,lfm2-1.2b)")
     parser.add_argument("--workload", choices=["decode", "serve", "mixed"], default="decode",
                         help="decode: the contract's line (default).  serve: 64 concurrent requests with prompts of "
                              "16..2048 tokens, 512-token portions, 128 new tokens each, through LLM.generate (use with "
@@ -312,6 +413,9 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.designs:
+        print(json.dumps(compare_designs(args)))
+        return 0
 
     import torch
 

@@ -49,8 +49,15 @@ def init_random(document: dict, seed: int, out: str, storage_dtype: str = "bfloa
 
     if num_layers is not None:
         document = dict(document)
-        document["layer_types"] = list(document["layer_types"])[:num_layers]
-        document["num_hidden_layers"] = num_layers
+        if "layer_types" in document:
+            document["layer_types"] = list(document["layer_types"])[:num_layers]
+            document["num_hidden_layers"] = num_layers
+        else:  # documents that list their layers as objects (a looped run is cut with them)
+            document["layers"] = list(document["layers"])[:num_layers]
+            if document.get("loop"):
+                loop = dict(document["loop"])
+                loop["start"], loop["stop"] = min(loop["start"], num_layers), min(loop["stop"], num_layers)
+                document["loop"] = loop
     _, _, plan = plan_from_document(document)
     model = Model(plan, BuildEnv(dtype=torch.float32, device=torch.device("cpu"), ops=None))
     write_model_folder(out, document, random_tensors(model.tensor_specs(), seed, std, storage_dtype))
