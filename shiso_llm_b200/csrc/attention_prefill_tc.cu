@@ -56,7 +56,9 @@ struct TcArgs {
     const int* block_table;  // [S, width]
     const int* q_start;      // [S + 1]
     const int* start_pos;    // [S]
-    __nv_bfloat16* out;      // [T, heads * 64]
+    __nv_bfloat16* out;      // [T, heads * 64], rows out_ld elements apart
+    float* log_sum;          // [T, heads] or null: the natural logarithm of each row's softmax sum
+    long long out_ld;
     int* status;
     int width, num_seqs, heads, kv_heads, page_size, window;
     int cache_rows;          // pages * page size: a row coordinate from here on reads zeros
@@ -362,7 +364,10 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (!mbar_wait(&pv_done[(num_tiles - 1) & 1], ((num_tiles - 1) >> 1) & 1)) failed = true;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;  // an empty span yields zeros
-        uint4* dst = reinterpret_cast<uint4*>(a.out + ((size_t)(first_token + r) * a.heads + head) * HEAD);
+        if (a.log_sum && r < rows)  // for a caller that folds further keys into the same softmax
+            a.log_sum[(size_t)(first_token + r) * a.heads + head] =
+                row_sum > 0.0f ? (row_max + log2f(row_sum)) * 0.6931471805599453f : -INFINITY;
+        uint4* dst = reinterpret_cast<uint4*>(a.out + (size_t)(first_token + r) * a.out_ld + (size_t)head * HEAD);
 #pragma unroll 1
         for (int c = 0; c < HEAD; c += 32) {
             uint32_t raw[32];
@@ -401,13 +406,27 @@ SHISO_API int shiso_prefill_attention_tc_supported(int head_dim, int page_size) 
            tc::encode_fn() != nullptr;
 }
 
-// q [T, heads * 64] bf16, caches [pages, page_size, kv_heads, 64] bf16, out [T, heads * 64].
+// A [rows, cols] bf16 view whose rows lie `ld` elements apart (a column range of a wider matrix),
+// as tiles of BQ x 64 with the 128B swizzle.  Encoded at every call: such views are not kept.
+static bool strided_map(const void* ptr, int rows, int cols, long long ld, CUtensorMap* out) {
+    tc::EncodeTiledFn encode = tc::encode_fn();
+    if (!encode || ((uintptr_t)ptr & 15)) return false;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {(cuuint32_t)tc::BK, (cuuint32_t)BQ};
+    cuuint32_t elem[2] = {1, 1};
+    return encode(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// q [T, heads * 64] bf16 with rows q_ld elements apart, caches [pages, page_size, kv_heads, 64] bf16,
+// out [T, heads * 64] with rows out_ld apart; log_sum [T, heads] float or null.
 // max_tiles: an upper bound on the number of 128-row query tiles over all sequences.
-SHISO_API int shiso_prefill_attention_tc(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
-                                         int table_width, const int* q_start, const int* start_pos, void* out,
-                                         int tokens, int num_seqs, int max_tiles, int heads, int kv_heads,
-                                         int page_size, long long num_pages, float scale, int window,
-                                         cudaStream_t stream) {
+static int launch_flash_tc(const void* q, long long q_ld, const void* k_cache, const void* v_cache, const int* block_table,
+                           int table_width, const int* q_start, const int* start_pos, void* out, long long out_ld,
+                           float* log_sum, int tokens, int num_seqs, int max_tiles, int heads, int kv_heads, int page_size,
+                           long long num_pages, float scale, int window, cudaStream_t stream) {
     if (num_seqs <= 0 || max_tiles <= 0 || tokens <= 0) return SHISO_OK;
     if (kv_heads <= 0 || heads % kv_heads) return SHISO_ERR_SHAPE;
     if (!shiso_prefill_attention_tc_supported(HEAD, page_size) || max_tiles > 65535) return SHISO_ERR_UNSUPPORTED;
@@ -415,7 +434,8 @@ SHISO_API int shiso_prefill_attention_tc(const void* q, const void* k_cache, con
     const long long cache_rows = num_pages * page_size;
     if (cache_rows + page_size > 0x7fffffffLL) return SHISO_ERR_UNSUPPORTED;
     CUtensorMap mq, mk, mv;
-    if (!tc::tensor_map(q, tokens, heads * HEAD, BQ, &mq) || !tc::tensor_map_paged(k_cache, cache_rows, kv_heads, page_size, &mk) ||
+    if ((q_ld % 8) || (out_ld % 8)) return SHISO_ERR_ALIGN;
+    if (!(q_ld == heads * HEAD ? tc::tensor_map(q, tokens, heads * HEAD, BQ, &mq) : strided_map(q, tokens, heads * HEAD, q_ld, &mq)) || !tc::tensor_map_paged(k_cache, cache_rows, kv_heads, page_size, &mk) ||
         !tc::tensor_map_paged(v_cache, cache_rows, kv_heads, page_size, &mv))
         return SHISO_ERR_UNSUPPORTED;
     TcArgs a;
@@ -423,6 +443,8 @@ SHISO_API int shiso_prefill_attention_tc(const void* q, const void* k_cache, con
     a.q_start = q_start;
     a.start_pos = start_pos;
     a.out = (__nv_bfloat16*)out;
+    a.log_sum = log_sum;
+    a.out_ld = out_ld;
     a.status = shiso_tc_status_word();
     a.width = table_width;
     a.num_seqs = num_seqs;
@@ -451,4 +473,25 @@ SHISO_API int shiso_prefill_attention_tc(const void* q, const void* k_cache, con
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     return (int)cudaLaunchKernelEx(&cfg, flash_tc_kernel, mq, mk, mv, a);
+}
+
+SHISO_API int shiso_prefill_attention_tc(const void* q, const void* k_cache, const void* v_cache, const int* block_table,
+                                         int table_width, const int* q_start, const int* start_pos, void* out,
+                                         int tokens, int num_seqs, int max_tiles, int heads, int kv_heads,
+                                         int page_size, long long num_pages, float scale, int window,
+                                         cudaStream_t stream) {
+    return launch_flash_tc(q, (long long)heads * HEAD, k_cache, v_cache, block_table, table_width, q_start, start_pos, out,
+                           (long long)heads * HEAD, nullptr, tokens, num_seqs, max_tiles, heads, kv_heads, page_size, num_pages,
+                           scale, window, stream);
+}
+
+// The same with queries and outputs that are column ranges of wider rows, and with the logarithm of
+// every row's softmax sum written out: a caller folds further keys into the same softmax afterwards.
+SHISO_API int shiso_prefill_attention_tc_open(const void* q, long long q_ld, const void* k_cache, const void* v_cache,
+                                              const int* block_table, int table_width, const int* q_start, const int* start_pos,
+                                              void* out, long long out_ld, float* log_sum, int tokens, int num_seqs,
+                                              int max_tiles, int heads, int kv_heads, int page_size, long long num_pages,
+                                              float scale, int window, cudaStream_t stream) {
+    return launch_flash_tc(q, q_ld, k_cache, v_cache, block_table, table_width, q_start, start_pos, out, out_ld, log_sum, tokens,
+                           num_seqs, max_tiles, heads, kv_heads, page_size, num_pages, scale, window, stream);
 }

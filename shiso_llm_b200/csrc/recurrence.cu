@@ -18,8 +18,11 @@
 //
 // Thread layout: a value column j of the state belongs to SPLIT neighbouring lanes, each
 // holding the rows i = ii * SPLIT + part in registers; the SPLIT partial sums of o_j meet in
-// two shuffles.  q, k and the decays of a token are staged in shared memory (two buffers, so
-// one barrier per token for them and one for the RMS).
+// two shuffles.  q, k and the decays of eight tokens at a time are staged in shared memory; a
+// thread walks the eight tokens over its rows of the state without meeting the others, so a
+// batch costs two barriers (the staged batch; the sums of squares of its eight outputs), and what
+// the next batch brings is asked for from global memory while this one is walked.  The sums a
+// token takes part in and their order are the same whatever the batch: cuts change no bit.
 #include "common.cuh"
 
 constexpr int REC_MAX_DIM = 256;
@@ -41,20 +44,27 @@ struct RecurrenceArgs {
 // Threads a CTA may have so that RPT rows of the state (and what else a thread needs) stay in registers.
 constexpr int rec_max_threads(int rpt) { return rpt <= 32 ? 512 : (rpt <= 128 ? 256 : 128); }
 
+constexpr int REC_BATCH = 8;   // tokens staged and walked between two barriers
+constexpr int REC_STAGED = 4;  // channels of q and k a thread stages per batch, at most
+
 template <typename AT, int RPT, int SPLIT, bool CHANNEL>
 __global__ void __launch_bounds__(rec_max_threads(RPT)) decay_recurrence_kernel(const RecurrenceArgs a) {
-    __shared__ float sq[2][REC_MAX_DIM], sk[2][REC_MAX_DIM], sw[2][REC_MAX_DIM], su[REC_MAX_DIM];
-    __shared__ float red[2][32];
+    __shared__ float sq[REC_BATCH][REC_MAX_DIM], sk[REC_BATCH][REC_MAX_DIM], sw[CHANNEL ? REC_BATCH : 1][REC_MAX_DIM];
+    __shared__ float su[REC_MAX_DIM];
+    __shared__ float red[REC_BATCH][32];
     const int head = blockIdx.x, seq = blockIdx.y;
-    const int tid = threadIdx.x;
+    const int tid = threadIdx.x, threads = blockDim.x;
     const int j = tid / SPLIT, part = tid % SPLIT;
     const int dim = a.dim, vdim = a.vdim;
     const int rpt = dim / SPLIT;  // rows of the state per thread (dim is a multiple of SPLIT)
     const bool owns = j < vdim;
-    const int lane = tid & 31, warp = tid >> 5, nwarps = (blockDim.x + 31) >> 5;
+    const int lane = tid & 31, warp = tid >> 5, nwarps = (threads + 31) >> 5;
+    // tokens per batch: what the threads can stage with REC_STAGED channels each (at least two:
+    // the CTA has half as many threads as there are key channels)
+    const int batch = min(REC_BATCH, REC_STAGED * threads / dim);
 
     if (CHANNEL)
-        for (int c = tid; c < dim; c += blockDim.x) su[c] = a.bonus[head * dim + c];
+        for (int c = tid; c < dim; c += threads) su[c] = a.bonus[head * dim + c];
     const float head_decay = CHANNEL ? 0.0f : a.head_decay[head];
     pdl_wait();
     const int first = a.q_start[seq], last = a.q_start[seq + 1];
@@ -71,62 +81,112 @@ __global__ void __launch_bounds__(rec_max_threads(RPT)) decay_recurrence_kernel(
     AT* out = (AT*)a.out + (size_t)head * vdim;
     const int half = a.rotary_dim / 2;
 
-    for (int t = first; t < last; ++t) {
-        const int b = (t - first) & 1;
-        for (int c = tid; c < dim; c += blockDim.x) {
-            float qc = to_f32(q[(size_t)t * a.q_ld + c]);
-            float kc = to_f32(k[(size_t)t * a.k_ld + c]);
+    // What a batch of tokens brings is asked for one batch ahead: the loads are in flight while the
+    // state walks the batch before.  Element e of a batch is channel e % dim of its token e / dim.
+    struct Raw { float q[REC_STAGED], k[REC_STAGED], q_other[REC_STAGED], k_other[REC_STAGED], v[REC_BATCH]; };
+    auto fetch = [&](int t0, int n, Raw& r) {
+#pragma unroll
+        for (int l = 0; l < REC_STAGED; ++l) {
+            const int e = tid + l * threads;
+            r.q[l] = r.k[l] = r.q_other[l] = r.k_other[l] = 0.0f;
+            if (e < n * dim) {
+                const int t = t0 + e / dim, c = e % dim;
+                r.q[l] = to_f32(q[(size_t)t * a.q_ld + c]);
+                r.k[l] = to_f32(k[(size_t)t * a.k_ld + c]);
+                if (CHANNEL) {
+                    r.q_other[l] = a.decay_logits[(size_t)t * a.logits_ld + head * dim + c];
+                } else if (c < a.rotary_dim) {
+                    const int other = c < half ? c + half : c - half;
+                    r.q_other[l] = to_f32(q[(size_t)t * a.q_ld + other]);
+                    r.k_other[l] = to_f32(k[(size_t)t * a.k_ld + other]);
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < REC_BATCH; ++i) r.v[i] = (owns && i < n) ? to_f32(v[(size_t)(t0 + i) * a.v_ld + j]) : 0.0f;
+    };
+    auto stage = [&](int t0, int n, const Raw& r) {
+#pragma unroll
+        for (int l = 0; l < REC_STAGED; ++l) {
+            const int e = tid + l * threads;
+            if (e >= n * dim) continue;
+            const int i = e / dim, c = e % dim;
+            float qc = r.q[l], kc = r.k[l];
             if (!CHANNEL) {
                 if (c < a.rotary_dim) {
-                    const int pair = c < half ? c : c - half;
-                    const int other = c < half ? c + half : c - half;
                     float sn, cs;
-                    sincosf((float)a.positions[t] * a.inv_freq[pair], &sn, &cs);
-                    const float qo = to_f32(q[(size_t)t * a.q_ld + other]), ko = to_f32(k[(size_t)t * a.k_ld + other]);
-                    qc = c < half ? qc * cs - qo * sn : qc * cs + qo * sn;
-                    kc = c < half ? kc * cs - ko * sn : kc * cs + ko * sn;
+                    sincosf((float)a.positions[t0 + i] * a.inv_freq[c < half ? c : c - half], &sn, &cs);
+                    qc = c < half ? qc * cs - r.q_other[l] * sn : qc * cs + r.q_other[l] * sn;
+                    kc = c < half ? kc * cs - r.k_other[l] * sn : kc * cs + r.k_other[l] * sn;
                 }
                 kc *= a.key_scale;
             } else {
-                sw[b][c] = expf(-expf(a.decay_logits[(size_t)t * a.logits_ld + head * dim + c] + a.decay_bias[head * dim + c]));
+                sw[i][c] = expf(-expf(r.q_other[l] + a.decay_bias[head * dim + c]));
             }
-            sq[b][c] = qc;
-            sk[b][c] = kc;
+            sq[i][c] = qc;
+            sk[i][c] = kc;
         }
-        const float vj = owns ? to_f32(v[(size_t)t * a.v_ld + j]) : 0.0f;
-        __syncthreads();
-        float o = 0.0f;
+    };
+    Raw cur, next;
+    fetch(first, min(batch, last - first), cur);
+    stage(first, min(batch, last - first), cur);
+    for (int t0 = first; t0 < last; t0 += batch) {
+        const int n = min(batch, last - t0);
+        const int n_next = min(batch, last - t0 - n);
+        if (n_next > 0) fetch(t0 + n, n_next, next);
+        __syncthreads();  // the batch is staged
+        float o[REC_BATCH];
 #pragma unroll
-        for (int ii = 0; ii < RPT; ++ii) {
-            if (ii < rpt) {
-                const int i = ii * SPLIT + part;
-                const float kv = sk[b][i] * vj;
-                if (CHANNEL) {
-                    o += sq[b][i] * (S[ii] + su[i] * kv);
-                    S[ii] = sw[b][i] * S[ii] + kv;
-                } else {
-                    S[ii] = head_decay * S[ii] + kv;
-                    o += sq[b][i] * S[ii];
+        for (int i = 0; i < REC_BATCH; ++i) {
+            o[i] = 0.0f;
+            if (i < n) {
+                const float vj = cur.v[i];
+#pragma unroll
+                for (int ii = 0; ii < RPT; ++ii) {
+                    if (ii < rpt) {
+                        const int row = ii * SPLIT + part;
+                        const float kv = sk[i][row] * vj;
+                        if (CHANNEL) {
+                            o[i] += sq[i][row] * (S[ii] + su[row] * kv);
+                            S[ii] = sw[i][row] * S[ii] + kv;
+                        } else {
+                            S[ii] = head_decay * S[ii] + kv;
+                            o[i] += sq[i][row] * S[ii];
+                        }
+                    }
                 }
             }
         }
 #pragma unroll
-        for (int off = 1; off < SPLIT; off <<= 1) o += __shfl_xor_sync(0xffffffffu, o, off);
-        const float mine = (owns && part == 0) ? o * o : 0.0f;
-        const float partial = warp_sum(mine);
-        if (lane == 0) red[b][warp] = partial;
-        __syncthreads();
-        float squares = 0.0f;
-        for (int w = 0; w < nwarps; ++w) squares += red[b][w];
-        if (owns && part == 0) {
-            float y = o * rsqrtf(squares / (float)vdim + a.eps);
-            if (a.out_weight) y *= a.out_weight[head * vdim + j];
-            if (gate) {
-                const float g = to_f32(gate[(size_t)t * a.gate_ld + j]);
-                y *= g / (1.0f + expf(-g));
-            }
-            out[(size_t)t * a.out_ld + j] = from_f32<AT>(y * a.out_scale);
+        for (int i = 0; i < REC_BATCH; ++i) {
+#pragma unroll
+            for (int off = 1; off < SPLIT; off <<= 1) o[i] += __shfl_xor_sync(0xffffffffu, o[i], off);
+            const float partial = warp_sum((owns && part == 0) ? o[i] * o[i] : 0.0f);
+            if (lane == 0) red[i][warp] = partial;
         }
+        __syncthreads();  // every thread has read the staged batch; the sums of squares are written
+        if (owns && part == 0) {
+#pragma unroll
+            for (int i = 0; i < REC_BATCH; ++i) {
+                if (i < n) {
+                    float squares = 0.0f;
+                    for (int w = 0; w < nwarps; ++w) squares += red[i][w];
+                    float y = o[i] * rsqrtf(squares / (float)vdim + a.eps);
+                    if (a.out_weight) y *= a.out_weight[head * vdim + j];
+                    if (gate) {
+                        const float g = to_f32(gate[(size_t)(t0 + i) * a.gate_ld + j]);
+                        y *= g / (1.0f + expf(-g));
+                    }
+                    out[(size_t)(t0 + i) * a.out_ld + j] = from_f32<AT>(y * a.out_scale);
+                }
+            }
+        }
+        if (n_next > 0) {
+            stage(t0 + n, n_next, next);
+            cur = next;
+        }
+        // (the next batch's first barrier orders these writes before its reads, and this batch's
+        // reads of the sums before their next writes)
     }
     pdl_trigger();
 #pragma unroll
@@ -137,7 +197,9 @@ __global__ void __launch_bounds__(rec_max_threads(RPT)) decay_recurrence_kernel(
 template <typename AT, int SPLIT, bool CHANNEL>
 static int launch_recurrence(const RecurrenceArgs& a, int num_seqs, cudaStream_t stream) {
     const int rpt = a.dim / SPLIT;
-    const unsigned threads = (unsigned)((a.vdim * SPLIT + 31) / 32 * 32);
+    // a thread per lane of a column, and at least half as many threads as key channels (they stage q and k)
+    const int columns = (a.vdim * SPLIT + 31) / 32 * 32, stagers = ((a.dim + 1) / 2 + 31) / 32 * 32;
+    const unsigned threads = (unsigned)(columns > stagers ? columns : stagers);
     const dim3 grid(a.heads, num_seqs);
 #define SHISO_REC(R)                                                                                          \
     if constexpr (R * SPLIT <= REC_MAX_DIM) {                                                                 \
@@ -163,8 +225,8 @@ static int rows_bucket(int rpt) {
 static int choose_split(int dim, int vdim) {
     for (int split = 4; split >= 1; split /= 2) {
         if (dim % split || dim / split < 1) continue;
-        const int threads = (vdim * split + 31) / 32 * 32;
-        if (threads <= rec_max_threads(rows_bucket(dim / split))) return split;
+        const int columns = (vdim * split + 31) / 32 * 32, stagers = ((dim + 1) / 2 + 31) / 32 * 32;
+        if ((columns > stagers ? columns : stagers) <= rec_max_threads(rows_bucket(dim / split))) return split;
     }
     return 0;
 }

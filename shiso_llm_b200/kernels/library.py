@@ -66,7 +66,8 @@ _SIGNATURES = {
     "shiso_decay_recurrence": [P, P, P, P, LL, LL, LL, LL, P, LL, I, P, LL, P, P, P, P, LL, P, P, P, P, I, F, P, F, F, I, I, I, I, P],
     "shiso_store_kv": [P, LL, P, LL, I, P, P, P, I, P, P, I, I, I, I, I, P],
     "shiso_pool_kv": [P, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, P],
-    "shiso_pooled_window_attention": [P, LL, I, P, P, P, P, P, P, I, P, P, P, LL, I, I, I, I, I, I, F, I, I, F, P],
+    "shiso_pooled_window_attention": [P, LL, I, P, P, P, P, P, P, I, P, P, P, LL, P, I, I, I, I, I, I, F, I, I, F, P],
+    "shiso_prefill_attention_tc_open": [P, LL, P, P, P, I, P, P, P, LL, P, I, I, I, I, I, I, LL, F, I, P],
 }
 
 

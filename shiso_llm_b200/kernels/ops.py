@@ -1068,12 +1068,35 @@ def pooled_window_attention(q, heads, k_cache, v_cache, block_table, pooled_k, p
     _check(pooled_table, "pooled block table", torch.int32, 2)
     if pooled_table.shape != block_table.shape:
         raise KernelError("the two block tables of a step have one shape")
-    status = library().shiso_pooled_window_attention(
+    lib = library()
+    tokens = q.shape[0]
+    seen = None
+    if (
+        act == torch.bfloat16 and dim == vdim and tokens >= TC_ATTENTION_MIN_TOKENS
+        and getattr(step, "max_q_len", tokens) >= TC_ATTENTION_MIN_PORTION
+        and lib.shiso_prefill_attention_tc_supported(dim, page_size) and q_ld % 8 == 0 and out_ld % 8 == 0
+        and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0
+    ):
+        # long portions: the window's tokens by the tensor-memory kernel, which leaves each row's
+        # normalised result and the logarithm of its softmax sum; the pooled blocks are folded in after
+        starts = getattr(step, "h_q_start", None)
+        if starts:
+            tiles = sum(-(-(b - a) // 128) for a, b in zip(starts[:-1], starts[1:]))
+        else:
+            tiles = tokens // 128 + step.num_seqs
+        seen = torch.empty((tokens, heads), dtype=torch.float32, device=q.device)
+        status = lib.shiso_prefill_attention_tc_open(
+            q.data_ptr(), q_ld, _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.q_start),
+            _ptr(step.start_pos), out.data_ptr(), out_ld, _ptr(seen), tokens, step.num_seqs, tiles, heads, kv_heads, page_size,
+            k_cache.shape[0], float(scale), int(window), _stream(),
+        )
+        _done(status, "prefill_attention (tcgen05, window of pooled_window_attention)", shape=(tokens, heads, dim))
+    status = lib.shiso_pooled_window_attention(
         q.data_ptr(), q_ld, _CODES[act], _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(pooled_k), _ptr(pooled_v),
         _ptr(pooled_table), block_table.shape[1], _ptr(step.positions), _ptr(step.seq_of_token), out.data_ptr(), out_ld,
-        q.shape[0], heads, kv_heads, dim, vdim, page_size, float(scale), int(window), int(pool), float(out_scale), _stream(),
+        _ptr(seen), tokens, heads, kv_heads, dim, vdim, page_size, float(scale), int(window), int(pool), float(out_scale), _stream(),
     )
-    _done(status, "pooled_window_attention", shape=(q.shape[0], heads, dim))
+    _done(status, "pooled_window_attention" + (" (pooled blocks)" if seen is not None else ""), shape=(tokens, heads, dim))
     return out
 
 
