@@ -146,7 +146,7 @@ template <typename CT>
 __device__ __forceinline__ void fold_chunk(const CT* __restrict__ k_cache, const CT* __restrict__ v_cache, const int* pages,
                                            int first, int count, int base, int page_size, int kv_heads, int kv_head, int dim,
                                            int vdim, const float* q, float scale, float& running_max, float& running_sum,
-                                           float (&acc)[PWA_PAIRS][2], int lane) {
+                                           float (&acc)[PWA_PAIRS][2], int lane, float* run_weight, long long* run_row) {
     const int n = min(32, count - base);
     long long row = -1;
     float score = -INFINITY;
@@ -171,13 +171,18 @@ __device__ __forceinline__ void fold_chunk(const CT* __restrict__ k_cache, const
         acc[e][1] *= keep;
     }
     const bool paired = vdim % 2 == 0;
+    // the run's weights and rows go through the warp's shared memory: every lane reads them all
+    __syncwarp();
+    run_weight[lane] = weight;
+    run_row[lane] = row >= 0 ? ((long long)row * kv_heads + kv_head) * vdim : -1;
+    __syncwarp();
     // (unrolled, so that the value rows of eight keys are asked for together)
 #pragma unroll 8
     for (int kk = 0; kk < 32; ++kk) {
-        const float w = __shfl_sync(0xffffffffu, weight, kk);
-        const long long r = __shfl_sync(0xffffffffu, row, kk);
+        const long long r = run_row[kk];
         if (r < 0) continue;  // also every lane beyond the run's keys
-        const CT* value = v_cache + ((size_t)r * kv_heads + kv_head) * vdim;
+        const float w = run_weight[kk];
+        const CT* value = v_cache + r;
 #pragma unroll
         for (int e = 0; e < PWA_PAIRS; ++e) {
             const int c = e * 64 + 2 * lane;
@@ -209,6 +214,8 @@ pooled_window_attention_kernel(const AT* __restrict__ q, long long q_ld, const A
                                long long out_ld, const float* __restrict__ seen, int heads, int kv_heads, int dim, int vdim,
                                int page_size, float scale, int window, int pool, float out_scale) {
     __shared__ float sq[PWA_MAX_DIM];
+    __shared__ float run_weight[PWA_WARPS][32];
+    __shared__ long long run_row[PWA_WARPS][32];
     __shared__ float part_max[PWA_WARPS], part_sum[PWA_WARPS];
     __shared__ float part_acc[PWA_WARPS][PWA_MAX_DIM];
     pdl_begin();
@@ -230,10 +237,11 @@ pooled_window_attention_kernel(const AT* __restrict__ q, long long q_ld, const A
     for (int run = warp; run < pooled_runs + token_runs; run += PWA_WARPS) {
         if (run < pooled_runs)
             fold_chunk<float>(pooled_k, pooled_v, pooled_table + (size_t)seq * table_width, 0, blocks, run * 32, page_size, kv_heads,
-                              kv_head, dim, vdim, sq, scale, running_max, running_sum, acc, lane);
+                              kv_head, dim, vdim, sq, scale, running_max, running_sum, acc, lane, run_weight[warp], run_row[warp]);
         else
             fold_chunk<AT>(k_cache, v_cache, table + (size_t)seq * table_width, first, tokens_seen, (run - pooled_runs) * 32,
-                           page_size, kv_heads, kv_head, dim, vdim, sq, scale, running_max, running_sum, acc, lane);
+                           page_size, kv_heads, kv_head, dim, vdim, sq, scale, running_max, running_sum, acc, lane, run_weight[warp],
+                           run_row[warp]);
     }
     if (lane == 0) {
         part_max[warp] = running_max;
@@ -284,6 +292,8 @@ pooled_blocks_merge_kernel(const AT* __restrict__ q, long long q_ld, const float
                            const float* __restrict__ seen, int tokens, int heads, int kv_heads, int dim, int vdim, int page_size,
                            float scale, int window, int pool, float out_scale) {
     __shared__ float sq[PWA_WARPS][PWA_MAX_DIM];
+    __shared__ float run_weight[PWA_WARPS][32];
+    __shared__ long long run_row[PWA_WARPS][32];
     pdl_begin();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long item = (long long)blockIdx.x * PWA_WARPS + warp;
@@ -303,7 +313,7 @@ pooled_blocks_merge_kernel(const AT* __restrict__ q, long long q_ld, const float
         __syncwarp();
         for (int base = 0; base < blocks; base += 32)
             fold_chunk<float>(pooled_k, pooled_v, pooled_table + (size_t)seq * table_width, 0, blocks, base, page_size, kv_heads,
-                              kv_head, dim, vdim, sq[warp], scale, running_max, running_sum, acc, lane);
+                              kv_head, dim, vdim, sq[warp], scale, running_max, running_sum, acc, lane, run_weight[warp], run_row[warp]);
     }
     const float before = seen[(size_t)t * heads + head];
     const float top = fmaxf(before, running_max);

@@ -4,20 +4,24 @@
 // sequence's rows of this step in order, so a position's output does not depend on how the
 // sequence was cut into steps or on what else is in the batch.  Two forms:
 //
+// A decay w multiplies the state as S - (1 - w) S with 1 - w formed directly (expm1f; the host
+// hands over 1 - decay_h): a decay close to 1 rounded to float32 as such would be off by 2^-24 of
+// itself per step, which a thousand steps multiply, while 1 - w keeps its own 24 bits.
+//
 //   channel decay (time mixing of the RWKV family)
 //       w_t = exp(-exp(logit_t + bias))                       per key channel
 //       o_t = (S_{t-1} + diag(bonus) k_t v_t^T)^T q_t
 //       S_t = diag(w_t) S_{t-1} + k_t v_t^T
 //   head decay (retention)
 //       q_t, k_t rotated by the position (half-split pairs), k_t times key_scale
-//       S_t = decay_h S_{t-1} + k_t v_t^T
+//       S_t = decay_h S_{t-1} + k_t v_t^T                 (head_loss = 1 - decay_h is what is handed over)
 //       o_t = S_t^T q_t
 //
 // then, for both, o_t brought to unit RMS over the head's value channels, times an optional
 // weight, times silu(gate), times a constant, rounded to the activation type.
 //
 // Thread layout: a value column j of the state belongs to SPLIT neighbouring lanes, each
-// holding the rows i = ii * SPLIT + part in registers; the SPLIT partial sums of o_j meet in
+// holding dim / SPLIT neighbouring rows in registers; the SPLIT partial sums of o_j meet in
 // two shuffles.  q, k and the decays of eight tokens at a time are staged in shared memory; a
 // thread walks the eight tokens over its rows of the state without meeting the others, so a
 // batch costs two barriers (the staged batch; the sums of squares of its eight outputs), and what
@@ -35,7 +39,7 @@ struct RecurrenceArgs {
     float* state; long long state_stride;  // [slots][heads][dim][vdim], slots `state_stride` floats apart
     const int* q_start; const int* slots; const int* positions;
     const float* decay_logits; long long logits_ld; const float* decay_bias; const float* bonus;  // channel decay
-    const float* head_decay; const float* inv_freq; int rotary_dim; float key_scale;               // head decay
+    const float* head_loss; const float* inv_freq; int rotary_dim; float key_scale;               // head decay
     const float* out_weight;
     float eps, out_scale;
     int heads, dim, vdim;
@@ -49,8 +53,8 @@ constexpr int REC_STAGED = 4;  // channels of q and k a thread stages per batch,
 
 template <typename AT, int RPT, int SPLIT, bool CHANNEL>
 __global__ void __launch_bounds__(rec_max_threads(RPT)) decay_recurrence_kernel(const RecurrenceArgs a) {
-    __shared__ float sq[REC_BATCH][REC_MAX_DIM], sk[REC_BATCH][REC_MAX_DIM], sw[CHANNEL ? REC_BATCH : 1][REC_MAX_DIM];
-    __shared__ float su[REC_MAX_DIM];
+    __shared__ __align__(16) float sq[REC_BATCH][REC_MAX_DIM], sk[REC_BATCH][REC_MAX_DIM], sw[CHANNEL ? REC_BATCH : 1][REC_MAX_DIM];
+    __shared__ __align__(16) float su[REC_MAX_DIM];
     __shared__ float red[REC_BATCH][32];
     const int head = blockIdx.x, seq = blockIdx.y;
     const int tid = threadIdx.x, threads = blockDim.x;
@@ -65,32 +69,53 @@ __global__ void __launch_bounds__(rec_max_threads(RPT)) decay_recurrence_kernel(
 
     if (CHANNEL)
         for (int c = tid; c < dim; c += threads) su[c] = a.bonus[head * dim + c];
-    const float head_decay = CHANNEL ? 0.0f : a.head_decay[head];
+    const float head_loss = CHANNEL ? 0.0f : a.head_loss[head];  // 1 - decay
+    const int half = a.rotary_dim / 2;
+    // what a thread stages of every batch: element e = tid + l * threads is channel e % dim of token e / dim
+    int st_token[REC_STAGED], st_chan[REC_STAGED];
+    float st_const[REC_STAGED];  // the channel's decay bias, or its rotation frequency
+#pragma unroll
+    for (int l = 0; l < REC_STAGED; ++l) {
+        const int e = tid + l * threads;
+        st_token[l] = e / dim;
+        st_chan[l] = e % dim;
+        st_const[l] = 0.0f;
+        if (st_token[l] < batch) {
+            const int c = st_chan[l];
+            if (CHANNEL) st_const[l] = a.decay_bias[head * dim + c];
+            else if (c < a.rotary_dim) st_const[l] = a.inv_freq[c < half ? c : c - half];
+        }
+    }
+    const float out_weight = (a.out_weight && owns) ? a.out_weight[head * vdim + j] : 1.0f;
     pdl_wait();
     const int first = a.q_start[seq], last = a.q_start[seq + 1];
     if (last <= first) return;
+    __syncthreads();  // the bonus is staged
+    // a thread's rows of the state are neighbours: row = part * rpt + ii
+    const int row0 = part * rpt;
+    const bool wide = rpt % 4 == 0;  // its slices of the staged vectors are read 16 bytes at a time
     float* state = a.state + (long long)a.slots[seq] * a.state_stride + (size_t)head * dim * vdim;
     float S[RPT];
 #pragma unroll
-    for (int ii = 0; ii < RPT; ++ii) S[ii] = (owns && ii < rpt) ? state[(size_t)(ii * SPLIT + part) * vdim + j] : 0.0f;
+    for (int ii = 0; ii < RPT; ++ii) {
+        S[ii] = (owns && ii < rpt) ? state[(size_t)(row0 + ii) * vdim + j] : 0.0f;
+    }
 
     const AT* q = (const AT*)a.q + (size_t)head * dim;
     const AT* k = (const AT*)a.k + (size_t)head * dim;
     const AT* v = (const AT*)a.v + (size_t)head * vdim;
     const AT* gate = a.gate ? (const AT*)a.gate + (size_t)head * vdim : nullptr;
     AT* out = (AT*)a.out + (size_t)head * vdim;
-    const int half = a.rotary_dim / 2;
 
     // What a batch of tokens brings is asked for one batch ahead: the loads are in flight while the
-    // state walks the batch before.  Element e of a batch is channel e % dim of its token e / dim.
+    // state walks the batch before.
     struct Raw { float q[REC_STAGED], k[REC_STAGED], q_other[REC_STAGED], k_other[REC_STAGED], v[REC_BATCH]; };
     auto fetch = [&](int t0, int n, Raw& r) {
 #pragma unroll
         for (int l = 0; l < REC_STAGED; ++l) {
-            const int e = tid + l * threads;
             r.q[l] = r.k[l] = r.q_other[l] = r.k_other[l] = 0.0f;
-            if (e < n * dim) {
-                const int t = t0 + e / dim, c = e % dim;
+            if (st_token[l] < n) {
+                const int t = t0 + st_token[l], c = st_chan[l];
                 r.q[l] = to_f32(q[(size_t)t * a.q_ld + c]);
                 r.k[l] = to_f32(k[(size_t)t * a.k_ld + c]);
                 if (CHANNEL) {
@@ -108,23 +133,33 @@ __global__ void __launch_bounds__(rec_max_threads(RPT)) decay_recurrence_kernel(
     auto stage = [&](int t0, int n, const Raw& r) {
 #pragma unroll
         for (int l = 0; l < REC_STAGED; ++l) {
-            const int e = tid + l * threads;
-            if (e >= n * dim) continue;
-            const int i = e / dim, c = e % dim;
+            if (st_token[l] >= n) continue;
+            const int i = st_token[l], c = st_chan[l];
             float qc = r.q[l], kc = r.k[l];
             if (!CHANNEL) {
                 if (c < a.rotary_dim) {
                     float sn, cs;
-                    sincosf((float)a.positions[t0 + i] * a.inv_freq[c < half ? c : c - half], &sn, &cs);
+                    sincosf((float)a.positions[t0 + i] * st_const[l], &sn, &cs);
                     qc = c < half ? qc * cs - r.q_other[l] * sn : qc * cs + r.q_other[l] * sn;
                     kc = c < half ? kc * cs - r.k_other[l] * sn : kc * cs + r.k_other[l] * sn;
                 }
                 kc *= a.key_scale;
             } else {
-                sw[i][c] = expf(-expf(r.q_other[l] + a.decay_bias[head * dim + c]));
+                sw[i][c] = -expm1f(-expf(r.q_other[l] + st_const[l]));  // 1 - w, exact to the last bit also where w is close to 1
             }
             sq[i][c] = qc;
             sk[i][c] = kc;
+        }
+    };
+    // one row of the state takes one token
+    auto take = [&](int ii, float qv, float kval, float wv, float uv, float vj, float& o) {
+        const float kv = kval * vj;
+        if (CHANNEL) {
+            o += qv * (S[ii] + uv * kv);
+            S[ii] = fmaf(-wv, S[ii], S[ii]) + kv;
+        } else {
+            S[ii] = fmaf(-head_loss, S[ii], S[ii]) + kv;
+            o += qv * S[ii];
         }
     };
     Raw cur, next;
@@ -134,6 +169,10 @@ __global__ void __launch_bounds__(rec_max_threads(RPT)) decay_recurrence_kernel(
         const int n = min(batch, last - t0);
         const int n_next = min(batch, last - t0 - n);
         if (n_next > 0) fetch(t0 + n, n_next, next);
+        float gates[REC_BATCH];  // asked for now, needed after the batch is walked
+#pragma unroll
+        for (int i = 0; i < REC_BATCH; ++i)
+            gates[i] = (gate && owns && part == 0 && i < n) ? to_f32(gate[(size_t)(t0 + i) * a.gate_ld + j]) : 0.0f;
         __syncthreads();  // the batch is staged
         float o[REC_BATCH];
 #pragma unroll
@@ -141,20 +180,31 @@ __global__ void __launch_bounds__(rec_max_threads(RPT)) decay_recurrence_kernel(
             o[i] = 0.0f;
             if (i < n) {
                 const float vj = cur.v[i];
+                // (the sum over a thread's rows runs in row order, as four interleaved chains)
+                float o4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                if (wide) {
 #pragma unroll
-                for (int ii = 0; ii < RPT; ++ii) {
-                    if (ii < rpt) {
-                        const int row = ii * SPLIT + part;
-                        const float kv = sk[i][row] * vj;
-                        if (CHANNEL) {
-                            o[i] += sq[i][row] * (S[ii] + su[row] * kv);
-                            S[ii] = sw[i][row] * S[ii] + kv;
-                        } else {
-                            S[ii] = head_decay * S[ii] + kv;
-                            o[i] += sq[i][row] * S[ii];
+                    for (int g4 = 0; g4 < RPT / 4; ++g4) {
+                        if (4 * g4 < rpt) {
+                            const float4 q4 = *reinterpret_cast<const float4*>(&sq[i][row0 + 4 * g4]);
+                            const float4 k4 = *reinterpret_cast<const float4*>(&sk[i][row0 + 4 * g4]);
+                            float4 w4 = make_float4(0.0f, 0.0f, 0.0f, 0.0f), u4 = w4;
+                            if (CHANNEL) {
+                                w4 = *reinterpret_cast<const float4*>(&sw[i][row0 + 4 * g4]);
+                                u4 = *reinterpret_cast<const float4*>(&su[row0 + 4 * g4]);
+                            }
+                            take(4 * g4 + 0, q4.x, k4.x, w4.x, u4.x, vj, o4[0]);
+                            take(4 * g4 + 1, q4.y, k4.y, w4.y, u4.y, vj, o4[1]);
+                            take(4 * g4 + 2, q4.z, k4.z, w4.z, u4.z, vj, o4[2]);
+                            take(4 * g4 + 3, q4.w, k4.w, w4.w, u4.w, vj, o4[3]);
                         }
                     }
+                } else {
+#pragma unroll
+                    for (int ii = 0; ii < RPT; ++ii)
+                        if (ii < rpt) take(ii, sq[i][row0 + ii], sk[i][row0 + ii], CHANNEL ? sw[i][row0 + ii] : 0.0f, CHANNEL ? su[row0 + ii] : 0.0f, vj, o4[ii & 3]);
                 }
+                o[i] = (o4[0] + o4[1]) + (o4[2] + o4[3]);
             }
         }
 #pragma unroll
@@ -171,12 +221,8 @@ __global__ void __launch_bounds__(rec_max_threads(RPT)) decay_recurrence_kernel(
                 if (i < n) {
                     float squares = 0.0f;
                     for (int w = 0; w < nwarps; ++w) squares += red[i][w];
-                    float y = o[i] * rsqrtf(squares / (float)vdim + a.eps);
-                    if (a.out_weight) y *= a.out_weight[head * vdim + j];
-                    if (gate) {
-                        const float g = to_f32(gate[(size_t)(t0 + i) * a.gate_ld + j]);
-                        y *= g / (1.0f + expf(-g));
-                    }
+                    float y = o[i] * rsqrtf(squares / (float)vdim + a.eps) * out_weight;
+                    if (gate) y *= gates[i] / (1.0f + expf(-gates[i]));
                     out[(size_t)(t0 + i) * a.out_ld + j] = from_f32<AT>(y * a.out_scale);
                 }
             }
@@ -191,7 +237,7 @@ __global__ void __launch_bounds__(rec_max_threads(RPT)) decay_recurrence_kernel(
     pdl_trigger();
 #pragma unroll
     for (int ii = 0; ii < RPT; ++ii)
-        if (owns && ii < rpt) state[(size_t)(ii * SPLIT + part) * vdim + j] = S[ii];
+        if (owns && ii < rpt) state[(size_t)(row0 + ii) * vdim + j] = S[ii];
 }
 
 template <typename AT, int SPLIT, bool CHANNEL>
@@ -249,13 +295,13 @@ SHISO_API int shiso_decay_recurrence(const void* q, const void* k, const void* v
                                      long long v_ld, long long gate_ld, void* out, long long out_ld, int act_dtype, float* state,
                                      long long state_stride, const int* q_start, const int* slots, const int* positions,
                                      const float* decay_logits, long long logits_ld, const float* decay_bias, const float* bonus,
-                                     const float* head_decay, const float* inv_freq, int rotary_dim, float key_scale,
+                                     const float* head_loss, const float* inv_freq, int rotary_dim, float key_scale,
                                      const float* out_weight, float eps, float out_scale, int num_seqs, int heads, int dim,
                                      int vdim, cudaStream_t stream) {
     if (num_seqs <= 0 || heads <= 0) return SHISO_OK;
     if (dim <= 0 || vdim <= 0 || dim > REC_MAX_DIM || vdim > REC_MAX_DIM || dim * vdim > REC_MAX_STATE) return SHISO_ERR_SHAPE;
     const bool channel = decay_logits != nullptr;
-    if (channel == (head_decay != nullptr)) return SHISO_ERR_UNSUPPORTED;
+    if (channel == (head_loss != nullptr)) return SHISO_ERR_UNSUPPORTED;
     if (channel && (!decay_bias || !bonus)) return SHISO_ERR_UNSUPPORTED;
     if (rotary_dim && (channel || !inv_freq || rotary_dim % 2 || rotary_dim > dim)) return SHISO_ERR_UNSUPPORTED;
     RecurrenceArgs a;
@@ -264,7 +310,7 @@ SHISO_API int shiso_decay_recurrence(const void* q, const void* k, const void* v
     a.out = out; a.state = state; a.state_stride = state_stride;
     a.q_start = q_start; a.slots = slots; a.positions = positions;
     a.decay_logits = decay_logits; a.logits_ld = logits_ld; a.decay_bias = decay_bias; a.bonus = bonus;
-    a.head_decay = head_decay; a.inv_freq = inv_freq; a.rotary_dim = rotary_dim; a.key_scale = key_scale;
+    a.head_loss = head_loss; a.inv_freq = inv_freq; a.rotary_dim = rotary_dim; a.key_scale = key_scale;
     a.out_weight = out_weight; a.eps = eps; a.out_scale = out_scale;
     a.heads = heads; a.dim = dim; a.vdim = vdim;
     if (act_dtype == SHISO_F32) return channel ? pick_split<float, true>(a, num_seqs, stream) : pick_split<float, false>(a, num_seqs, stream);

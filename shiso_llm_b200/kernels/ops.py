@@ -959,11 +959,13 @@ def recurrence_supported(dim: int, vdim: int) -> bool:
 
 
 def decay_recurrence(q, k, v, out, state, step, heads, dim, vdim, eps, *, decay_logits=None, decay_bias=None, bonus=None,
-                     head_decay=None, inv_freq=None, rotary_dim=0, key_scale=1.0, out_weight=None, gate=None, out_scale=1.0):
+                     head_decay=None, head_loss=None, inv_freq=None, rotary_dim=0, key_scale=1.0, out_weight=None, gate=None,
+                     out_scale=1.0):
     """A matrix state ``S[dim, vdim]`` per head (``state``, float32 ``[slots, heads, dim, vdim]``),
     walked over each sequence's rows in order.  With ``decay_logits`` (float32 ``[T, heads * dim]``),
     ``decay_bias`` and ``bonus``: ``w = exp(-exp(logits + bias))``, ``o = (S + diag(bonus) k v^T)^T q``,
-    then ``S = diag(w) S + k v^T``.  With ``head_decay`` (float32 ``[heads]``): q and k rotated by the
+    then ``S = diag(w) S + k v^T``.  With ``head_decay`` (float32 ``[heads]``; ``head_loss`` = 1 - decay, formed in higher
+    precision, is what the kernel multiplies by - when it is not given it is formed here): q and k rotated by the
     position (half-split pairs over ``rotary_dim``), k times ``key_scale``, ``S = decay S + k v^T``,
     then ``o = S^T q``.  ``o`` is brought to unit RMS per head, times ``out_weight``, times
     ``silu(gate)``, times ``out_scale``, into ``out``.  q, k, v, gate and out may be column ranges."""
@@ -986,6 +988,11 @@ def decay_recurrence(q, k, v, out, state, step, heads, dim, vdim, eps, *, decay_
         _check(head_decay, "head decay", torch.float32, 1)
         if head_decay.shape[0] != heads:
             raise KernelError(f"{head_decay.shape[0]} decays for {heads} heads")
+        if head_loss is None:
+            head_loss = (1.0 - head_decay.double()).float()
+        _check(head_loss, "head loss", torch.float32, 1)
+        if head_loss.shape[0] != heads:
+            raise KernelError(f"{head_loss.shape[0]} values of 1 - decay for {heads} heads")
     if rotary_dim:
         _check(inv_freq, "inv_freq", torch.float32, 1)
         if inv_freq.shape[0] != rotary_dim // 2:
@@ -997,7 +1004,7 @@ def decay_recurrence(q, k, v, out, state, step, heads, dim, vdim, eps, *, decay_
     status = library().shiso_decay_recurrence(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), gate.data_ptr() if gate is not None else 0, q_ld, k_ld, v_ld, gate_ld,
         out.data_ptr(), out_ld, _CODES[act], state.data_ptr(), stride, _ptr(step.q_start), _ptr(step.state_slots),
-        _ptr(step.positions), _ptr(decay_logits), logits_ld, _ptr(decay_bias), _ptr(bonus), _ptr(head_decay),
+        _ptr(step.positions), _ptr(decay_logits), logits_ld, _ptr(decay_bias), _ptr(bonus), _ptr(head_loss),
         _ptr(inv_freq) if rotary_dim else 0, int(rotary_dim), float(key_scale), _ptr(out_weight), float(eps), float(out_scale),
         step.num_seqs, heads, dim, vdim, _stream(),
     )

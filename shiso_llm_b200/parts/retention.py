@@ -49,7 +49,9 @@ class Retention(Mixer):
         fits = getattr(env.ops, "recurrence_supported", None)
         if fits is not None and not fits(self.dim, self.vdim):
             raise UnsupportedShape("head sizes", (self.dim, self.vdim), "the recurrence kernel has no layout for a state of this shape")
-        self.decays = torch.tensor(decays, dtype=torch.float32, device=env.device)
+        self.decays = torch.tensor(decays, dtype=torch.float64).to(torch.float32).to(env.device)
+        # what the kernel multiplies by: S - (1 - decay) S, with 1 - decay formed in float64
+        self.losses = (1.0 - torch.tensor(decays, dtype=torch.float64)).to(torch.float32).to(env.device)
         self.position = POSITION_ENCODINGS.build(p["position"], env, self.dim)
         if getattr(self.position, "interleaved", False):
             raise UnsupportedShape("position", p["position"].kind, "the recurrence kernel rotates half-split pairs")
@@ -94,7 +96,7 @@ class Retention(Mixer):
         self.env.ops.decay_recurrence(
             proj[:, :qk], proj[:, qk : 2 * qk], proj[:, 2 * qk : 2 * qk + vg], out, cache.state, step,
             self.heads, self.dim, self.vdim, self.eps,
-            head_decay=self.decays, inv_freq=inv_freq, rotary_dim=rotary_dim, key_scale=self.dim ** -0.5,
+            head_decay=self.decays, head_loss=self.losses, inv_freq=inv_freq, rotary_dim=rotary_dim, key_scale=self.dim ** -0.5,
             gate=proj[:, 2 * qk + vg :], out_scale=out_scale,
         )
 

@@ -323,7 +323,8 @@ def unary(x, kind, out_dtype):
 
 
 def decay_recurrence(q, k, v, out, state, step, heads, dim, vdim, eps, *, decay_logits=None, decay_bias=None, bonus=None,
-                     head_decay=None, inv_freq=None, rotary_dim=0, key_scale=1.0, out_weight=None, gate=None, out_scale=1.0):
+                     head_decay=None, head_loss=None, inv_freq=None, rotary_dim=0, key_scale=1.0, out_weight=None, gate=None,
+                     out_scale=1.0):
     """Per head ``S[dim, vdim]``.  With ``decay_logits``: ``w = exp(-exp(logits + bias))`` per key
     channel, ``o = (S + diag(bonus) k v^T)^T q`` and then ``S = diag(w) S + k v^T``.  With
     ``head_decay``: ``S = decay S + k v^T`` and then ``o = S^T q``; q and k are rotated (half-split
