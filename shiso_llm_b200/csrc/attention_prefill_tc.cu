@@ -63,6 +63,7 @@ struct TcArgs {
     int width, num_seqs, heads, kv_heads, page_size, window;
     int cache_rows;          // pages * page size: a row coordinate from here on reads zeros
     float scale_log2;        // scale * log2(e)
+    float out_scale;         // a constant the normalised result is multiplied by
 };
 
 __device__ __forceinline__ float ex2(float x) {
@@ -363,7 +364,7 @@ flash_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         pdl_trigger();
         if (!mbar_wait(&pv_done[(num_tiles - 1) & 1], ((num_tiles - 1) >> 1) & 1)) failed = true;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const float inv = row_sum > 0.0f ? 1.0f / row_sum : 0.0f;  // an empty span yields zeros
+        const float inv = row_sum > 0.0f ? a.out_scale / row_sum : 0.0f;  // an empty span yields zeros
         if (a.log_sum && r < rows)  // for a caller that folds further keys into the same softmax
             a.log_sum[(size_t)(first_token + r) * a.heads + head] =
                 row_sum > 0.0f ? (row_max + log2f(row_sum)) * 0.6931471805599453f : -INFINITY;
@@ -425,8 +426,8 @@ static bool strided_map(const void* ptr, int rows, int cols, long long ld, CUten
 // max_tiles: an upper bound on the number of 128-row query tiles over all sequences.
 static int launch_flash_tc(const void* q, long long q_ld, const void* k_cache, const void* v_cache, const int* block_table,
                            int table_width, const int* q_start, const int* start_pos, void* out, long long out_ld,
-                           float* log_sum, int tokens, int num_seqs, int max_tiles, int heads, int kv_heads, int page_size,
-                           long long num_pages, float scale, int window, cudaStream_t stream) {
+                           float* log_sum, float out_scale, int tokens, int num_seqs, int max_tiles, int heads, int kv_heads,
+                           int page_size, long long num_pages, float scale, int window, cudaStream_t stream) {
     if (num_seqs <= 0 || max_tiles <= 0 || tokens <= 0) return SHISO_OK;
     if (kv_heads <= 0 || heads % kv_heads) return SHISO_ERR_SHAPE;
     if (!shiso_prefill_attention_tc_supported(HEAD, page_size) || max_tiles > 65535) return SHISO_ERR_UNSUPPORTED;
@@ -454,6 +455,7 @@ static int launch_flash_tc(const void* q, long long q_ld, const void* k_cache, c
     a.window = window;
     a.cache_rows = (int)cache_rows;
     a.scale_log2 = scale * 1.4426950408889634f;
+    a.out_scale = out_scale;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(flash_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -481,17 +483,18 @@ SHISO_API int shiso_prefill_attention_tc(const void* q, const void* k_cache, con
                                          int page_size, long long num_pages, float scale, int window,
                                          cudaStream_t stream) {
     return launch_flash_tc(q, (long long)heads * HEAD, k_cache, v_cache, block_table, table_width, q_start, start_pos, out,
-                           (long long)heads * HEAD, nullptr, tokens, num_seqs, max_tiles, heads, kv_heads, page_size, num_pages,
+                           (long long)heads * HEAD, nullptr, 1.0f, tokens, num_seqs, max_tiles, heads, kv_heads, page_size, num_pages,
                            scale, window, stream);
 }
 
-// The same with queries and outputs that are column ranges of wider rows, and with the logarithm of
-// every row's softmax sum written out: a caller folds further keys into the same softmax afterwards.
+// The same with queries and outputs that are column ranges of wider rows, the result times
+// out_scale, and with the logarithm of every row's softmax sum written out: a caller folds
+// further keys into the same softmax afterwards.
 SHISO_API int shiso_prefill_attention_tc_open(const void* q, long long q_ld, const void* k_cache, const void* v_cache,
                                               const int* block_table, int table_width, const int* q_start, const int* start_pos,
-                                              void* out, long long out_ld, float* log_sum, int tokens, int num_seqs,
-                                              int max_tiles, int heads, int kv_heads, int page_size, long long num_pages,
-                                              float scale, int window, cudaStream_t stream) {
-    return launch_flash_tc(q, q_ld, k_cache, v_cache, block_table, table_width, q_start, start_pos, out, out_ld, log_sum, tokens,
+                                              void* out, long long out_ld, float* log_sum, float out_scale, int tokens,
+                                              int num_seqs, int max_tiles, int heads, int kv_heads, int page_size,
+                                              long long num_pages, float scale, int window, cudaStream_t stream) {
+    return launch_flash_tc(q, q_ld, k_cache, v_cache, block_table, table_width, q_start, start_pos, out, out_ld, log_sum, out_scale, tokens,
                            num_seqs, max_tiles, heads, kv_heads, page_size, num_pages, scale, window, stream);
 }

@@ -66,11 +66,13 @@ __global__ void pool_kv_kernel(const AT* __restrict__ k_cache, const AT* __restr
     const size_t to_row = (size_t)to_page * page_size + block % page_size;
     const int* pages = table + (size_t)seq * table_width;
     const int first = pos + 1 - pool;
-    for (int c = threadIdx.x; c < kw + vw; c += blockDim.x) {
+    // (the row's columns are spread over blockIdx.y: few rows of a step end a block)
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < kw + vw; c += gridDim.y * blockDim.x) {
         const bool key = c < kw;
         const AT* cache = key ? k_cache : v_cache;
         const int width = key ? kw : vw, col = key ? c : c - kw;
         float sum = 0.0f;
+#pragma unroll 4
         for (int p = first; p <= pos; ++p) {
             const int page = pages[p / page_size];
             sum += page < 0 ? 0.0f : to_f32(cache[((size_t)page * page_size + p % page_size) * width + col]);
@@ -85,11 +87,12 @@ SHISO_API int shiso_pool_kv(const void* k_cache, const void* v_cache, int cache_
                             cudaStream_t stream) {
     if (tokens <= 0) return SHISO_OK;
     if (pool < 1) return SHISO_ERR_SHAPE;
+    const dim3 grid(tokens, ceil_div_u((long long)kv_heads * (dim + vdim), 128) < 16 ? ceil_div_u((long long)kv_heads * (dim + vdim), 128) : 16);
     if (cache_dtype == SHISO_F32)
-        launch_kernel(pool_kv_kernel<float>, tokens, 128, 0, stream, (const float*)k_cache, (const float*)v_cache, table, pooled_k,
+        launch_kernel(pool_kv_kernel<float>, grid, 128, 0, stream, (const float*)k_cache, (const float*)v_cache, table, pooled_k,
                       pooled_v, pooled_table, table_width, positions, seq_of_token, kv_heads * dim, kv_heads * vdim, page_size, pool);
     else if (cache_dtype == SHISO_BF16)
-        launch_kernel(pool_kv_kernel<__nv_bfloat16>, tokens, 128, 0, stream, (const __nv_bfloat16*)k_cache,
+        launch_kernel(pool_kv_kernel<__nv_bfloat16>, grid, 128, 0, stream, (const __nv_bfloat16*)k_cache,
                       (const __nv_bfloat16*)v_cache, table, pooled_k, pooled_v, pooled_table, table_width, positions, seq_of_token,
                       kv_heads * dim, kv_heads * vdim, page_size, pool);
     else
@@ -203,15 +206,14 @@ __device__ __forceinline__ void fold_chunk(const CT* __restrict__ k_cache, const
 // One CTA per (row, query head).  The two lists - pooled blocks, then the window's tokens - are cut
 // into runs of 32 keys from each list's start; run c belongs to warp c % 8, and the warps' partial
 // softmaxes are merged in warp order.  What a row adds up, and in which order, depends on its
-// position only.  With `seen` (the logarithm of a softmax sum already taken over the window, whose
-// normalised output stands in `out`), only the pooled blocks are folded and merged with that.
+// position only.
 template <typename AT>
 __global__ void __launch_bounds__(PWA_WARPS * 32)
 pooled_window_attention_kernel(const AT* __restrict__ q, long long q_ld, const AT* __restrict__ k_cache,
                                const AT* __restrict__ v_cache, const int* __restrict__ table, const float* __restrict__ pooled_k,
                                const float* __restrict__ pooled_v, const int* __restrict__ pooled_table, int table_width,
                                const int* __restrict__ positions, const int* __restrict__ seq_of_token, AT* out,
-                               long long out_ld, const float* __restrict__ seen, int heads, int kv_heads, int dim, int vdim,
+                               long long out_ld, int heads, int kv_heads, int dim, int vdim,
                                int page_size, float scale, int window, int pool, float out_scale) {
     __shared__ float sq[PWA_MAX_DIM];
     __shared__ float run_weight[PWA_WARPS][32];
@@ -228,7 +230,7 @@ pooled_window_attention_kernel(const AT* __restrict__ q, long long q_ld, const A
     const int first = max(0, pos - window + 1);
     const int behind = pos - window + 1;  // positions before this one lie behind the window
     const int blocks = behind > 0 ? behind / pool : 0;
-    const int tokens_seen = seen ? 0 : pos - first + 1;
+    const int tokens_seen = pos - first + 1;
     const int pooled_runs = (blocks + 31) / 32, token_runs = (tokens_seen + 31) / 32;
     float running_max = -INFINITY, running_sum = 0.0f;
     float acc[PWA_PAIRS][2];
@@ -257,8 +259,7 @@ pooled_window_attention_kernel(const AT* __restrict__ q, long long q_ld, const A
     }
     __syncthreads();
     AT* dst = out + (size_t)t * out_ld + (size_t)head * vdim;
-    const float before = seen ? seen[(size_t)t * heads + head] : -INFINITY;  // log of the sum the window gave
-    float top = before;
+    float top = -INFINITY;
 #pragma unroll
     for (int w = 0; w < PWA_WARPS; ++w) top = fmaxf(top, part_max[w]);
     if (top == -INFINITY) {
@@ -266,15 +267,14 @@ pooled_window_attention_kernel(const AT* __restrict__ q, long long q_ld, const A
         return;
     }
     float factor[PWA_WARPS];
-    const float old = seen ? expf(before - top) : 0.0f;
-    float total = old;
+    float total = 0.0f;
 #pragma unroll
     for (int w = 0; w < PWA_WARPS; ++w) {
         factor[w] = part_max[w] == -INFINITY ? 0.0f : expf(part_max[w] - top);
         total += part_sum[w] * factor[w];
     }
     for (int c = threadIdx.x; c < vdim; c += blockDim.x) {
-        float sum = seen ? old * to_f32(dst[c]) : 0.0f;  // what stands there is normalised: times its share of the sum
+        float sum = 0.0f;
 #pragma unroll
         for (int w = 0; w < PWA_WARPS; ++w) sum += part_acc[w][c] * factor[w];
         dst[c] = from_f32<AT>(sum / total * out_scale);
@@ -282,7 +282,8 @@ pooled_window_attention_kernel(const AT* __restrict__ q, long long q_ld, const A
 }
 
 // The pooled blocks alone, folded into a softmax whose window part another kernel has taken:
-// `out` holds that part's normalised result and `seen` the logarithm of its sum.  A row sees few
+// `out` holds that part's normalised result, already times out_scale, and `seen` the logarithm of
+// its sum; a row that sees no block is finished as it stands.  A row sees few
 // blocks (its position / pool at most), so a warp takes a (row, head) by itself, eight to a CTA.
 template <typename AT>
 __global__ void __launch_bounds__(PWA_WARPS * 32)
@@ -303,12 +304,13 @@ pooled_blocks_merge_kernel(const AT* __restrict__ q, long long q_ld, const float
     const int pos = positions[t], seq = seq_of_token[t];
     const int behind = pos - window + 1;
     const int blocks = behind > 0 ? behind / pool : 0;
+    if (blocks <= 0) return;
     AT* dst = out + (size_t)t * out_ld + (size_t)head * vdim;
     float running_max = -INFINITY, running_sum = 0.0f;
     float acc[PWA_PAIRS][2];
 #pragma unroll
     for (int e = 0; e < PWA_PAIRS; ++e) acc[e][0] = acc[e][1] = 0.0f;
-    if (blocks > 0) {
+    {
         for (int c = lane; c < dim; c += 32) sq[warp][c] = to_f32(q[(size_t)t * q_ld + (size_t)head * dim + c]);
         __syncwarp();
         for (int base = 0; base < blocks; base += 32)
@@ -326,8 +328,8 @@ pooled_blocks_merge_kernel(const AT* __restrict__ q, long long q_ld, const float
         for (int h = 0; h < 2; ++h) {
             const int c = e * 64 + 2 * lane + h;
             if (c < vdim) {
-                const float sum = old * to_f32(dst[c]) + acc[e][h] * fresh;
-                dst[c] = from_f32<AT>(total > 0.0f ? sum / total * out_scale : 0.0f);
+                const float sum = old * to_f32(dst[c]) + acc[e][h] * fresh * out_scale;
+                dst[c] = from_f32<AT>(total > 0.0f ? sum / total : 0.0f);
             }
         }
     }
@@ -360,11 +362,11 @@ SHISO_API int shiso_pooled_window_attention(const void* q, long long q_ld, int a
     if (act_dtype == SHISO_F32)
         launch_kernel(pooled_window_attention_kernel<float>, blocks, PWA_WARPS * 32, 0, stream, (const float*)q, q_ld,
                       (const float*)k_cache, (const float*)v_cache, table, pooled_k, pooled_v, pooled_table, table_width, positions,
-                      seq_of_token, (float*)out, out_ld, seen, heads, kv_heads, dim, vdim, page_size, scale, window, pool, out_scale);
+                      seq_of_token, (float*)out, out_ld, heads, kv_heads, dim, vdim, page_size, scale, window, pool, out_scale);
     else if (act_dtype == SHISO_BF16)
         launch_kernel(pooled_window_attention_kernel<__nv_bfloat16>, blocks, PWA_WARPS * 32, 0, stream, (const __nv_bfloat16*)q, q_ld,
                       (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, table, pooled_k, pooled_v, pooled_table,
-                      table_width, positions, seq_of_token, (__nv_bfloat16*)out, out_ld, seen, heads, kv_heads, dim, vdim,
+                      table_width, positions, seq_of_token, (__nv_bfloat16*)out, out_ld, heads, kv_heads, dim, vdim,
                       page_size, scale, window, pool, out_scale);
     else
         return SHISO_ERR_DTYPE;

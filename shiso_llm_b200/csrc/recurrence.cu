@@ -22,7 +22,7 @@
 //
 // Thread layout: a value column j of the state belongs to SPLIT neighbouring lanes, each
 // holding dim / SPLIT neighbouring rows in registers; the SPLIT partial sums of o_j meet in
-// two shuffles.  q, k and the decays of eight tokens at a time are staged in shared memory; a
+// a few shuffles.  q, k and the decays of eight tokens at a time are staged in shared memory; a
 // thread walks the eight tokens over its rows of the state without meeting the others, so a
 // batch costs two barriers (the staged batch; the sums of squares of its eight outputs), and what
 // the next batch brings is asked for from global memory while this one is walked.  The sums a
@@ -172,7 +172,7 @@ __global__ void __launch_bounds__(rec_max_threads(RPT)) decay_recurrence_kernel(
         float gates[REC_BATCH];  // asked for now, needed after the batch is walked
 #pragma unroll
         for (int i = 0; i < REC_BATCH; ++i)
-            gates[i] = (gate && owns && part == 0 && i < n) ? to_f32(gate[(size_t)(t0 + i) * a.gate_ld + j]) : 0.0f;
+            gates[i] = (gate && owns && i % SPLIT == part && i < n) ? to_f32(gate[(size_t)(t0 + i) * a.gate_ld + j]) : 0.0f;
         __syncthreads();  // the batch is staged
         float o[REC_BATCH];
 #pragma unroll
@@ -215,10 +215,11 @@ __global__ void __launch_bounds__(rec_max_threads(RPT)) decay_recurrence_kernel(
             if (lane == 0) red[i][warp] = partial;
         }
         __syncthreads();  // every thread has read the staged batch; the sums of squares are written
-        if (owns && part == 0) {
+        if (owns) {
+            // (every lane of a column holds the column's sums: the lanes share the batch's tokens)
 #pragma unroll
             for (int i = 0; i < REC_BATCH; ++i) {
-                if (i < n) {
+                if (i % SPLIT == part && i < n) {
                     float squares = 0.0f;
                     for (int w = 0; w < nwarps; ++w) squares += red[i][w];
                     float y = o[i] * rsqrtf(squares / (float)vdim + a.eps) * out_weight;
@@ -266,10 +267,10 @@ static int rows_bucket(int rpt) {
     return REC_MAX_DIM;
 }
 
-// Into how many lanes a column of the state is split: as many (4, 2, 1) as divide the key size
+// Into how many lanes a column of the state is split: as many (8, 4, 2, 1) as divide the key size
 // and leave the CTA within the threads its rows per thread allow; 0 when nothing fits.
 static int choose_split(int dim, int vdim) {
-    for (int split = 4; split >= 1; split /= 2) {
+    for (int split = 8; split >= 1; split /= 2) {
         if (dim % split || dim / split < 1) continue;
         const int columns = (vdim * split + 31) / 32 * 32, stagers = ((dim + 1) / 2 + 31) / 32 * 32;
         if ((columns > stagers ? columns : stagers) <= rec_max_threads(rows_bucket(dim / split))) return split;
@@ -284,6 +285,7 @@ SHISO_API int shiso_decay_recurrence_supported(int dim, int vdim) {
 template <typename AT, bool CHANNEL>
 static int pick_split(const RecurrenceArgs& a, int num_seqs, cudaStream_t stream) {
     switch (choose_split(a.dim, a.vdim)) {
+        case 8: return launch_recurrence<AT, 8, CHANNEL>(a, num_seqs, stream);
         case 4: return launch_recurrence<AT, 4, CHANNEL>(a, num_seqs, stream);
         case 2: return launch_recurrence<AT, 2, CHANNEL>(a, num_seqs, stream);
         case 1: return launch_recurrence<AT, 1, CHANNEL>(a, num_seqs, stream);

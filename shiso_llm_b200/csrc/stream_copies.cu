@@ -4,6 +4,8 @@
 //
 // Everything here is float arithmetic on float streams; only the rows handed to a product are
 // rounded to the activation type.
+#include <type_traits>
+
 #include "common.cuh"
 
 // --------------------------------------------------------------------------- hashed-pair embedding
@@ -101,44 +103,78 @@ __global__ void hyper_mix_kernel(const float* src, long long src_stride, const A
     pdl_begin();
     const size_t at = (size_t)blockIdx.x * hidden;
     float squares = 0.0f;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-        float x[MAX_COPIES], nx[MAX_COPIES];
+    // W neighbouring elements a thread: 4 (16-byte loads and stores of the float copies) where rows allow it
+    auto walk = [&](auto width) {
+        constexpr int W = decltype(width)::value;
+        for (int i = threadIdx.x * W; i < hidden; i += blockDim.x * W) {
+            float x[MAX_COPIES][W], nx[MAX_COPIES][W];
 #pragma unroll
-        for (int s = 0; s < MAX_COPIES; ++s) x[s] = s < copies ? src[(size_t)s * src_stride + at + i] : 0.0f;
-        if (y) {
-            const float yy = to_f32(y[at + i]);
+            for (int s = 0; s < MAX_COPIES; ++s) {
+                if (s < copies) {
+                    const float* p = src + (size_t)s * src_stride + at + i;
+                    if (W == 4) {
+                        const float4 v = *reinterpret_cast<const float4*>(p);
+                        x[s][0] = v.x; x[s][W > 1 ? 1 : 0] = v.y; x[s][W > 2 ? 2 : 0] = v.z; x[s][W > 3 ? 3 : 0] = v.w;
+                    } else {
+                        x[s][0] = p[0];
+                    }
+                } else {
 #pragma unroll
-            for (int r = 0; r < MAX_COPIES; ++r) {
-                float v = 0.0f;
-                if (r < copies) {
-#pragma unroll
-                    for (int s = 0; s < MAX_COPIES; ++s)
-                        if (s < copies) v += s_mix[s * copies + r] * x[s];
-                    v += s_write[r] * yy;
-                    if (dst) dst[(size_t)r * dst_stride + at + i] = v;
+                    for (int e = 0; e < W; ++e) x[s][e] = 0.0f;
                 }
-                nx[r] = v;
             }
-        } else {
+            if (y) {
+                float yy[W];
 #pragma unroll
-            for (int r = 0; r < MAX_COPIES; ++r) nx[r] = x[r];
-        }
-        if (read) {
-            float u = 0.0f;
+                for (int e = 0; e < W; ++e) yy[e] = to_f32(y[at + i + e]);
 #pragma unroll
-            for (int r = 0; r < MAX_COPIES; ++r)
-                if (r < copies) u += s_read[r] * nx[r];
-            row_u[i] = u;
-            squares += u * u;
-        }
-        if (sum_out) {
-            float total = 0.0f;
+                for (int r = 0; r < MAX_COPIES; ++r) {
 #pragma unroll
-            for (int r = 0; r < MAX_COPIES; ++r)
-                if (r < copies) total += nx[r];
-            sum_out[at + i] = total;
+                    for (int e = 0; e < W; ++e) nx[r][e] = 0.0f;
+                    if (r < copies) {
+#pragma unroll
+                        for (int e = 0; e < W; ++e) {
+                            float v = 0.0f;
+#pragma unroll
+                            for (int s = 0; s < MAX_COPIES; ++s)
+                                if (s < copies) v += s_mix[s * copies + r] * x[s][e];
+                            nx[r][e] = v + s_write[r] * yy[e];
+                        }
+                        if (dst) {
+                            float* p = dst + (size_t)r * dst_stride + at + i;
+                            if (W == 4) *reinterpret_cast<float4*>(p) = make_float4(nx[r][0], nx[r][W > 1 ? 1 : 0], nx[r][W > 2 ? 2 : 0], nx[r][W > 3 ? 3 : 0]);
+                            else p[0] = nx[r][0];
+                        }
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < MAX_COPIES; ++r)
+#pragma unroll
+                    for (int e = 0; e < W; ++e) nx[r][e] = x[r][e];
+            }
+#pragma unroll
+            for (int e = 0; e < W; ++e) {
+                if (read) {
+                    float u = 0.0f;
+#pragma unroll
+                    for (int r = 0; r < MAX_COPIES; ++r)
+                        if (r < copies) u += s_read[r] * nx[r][e];
+                    row_u[i + e] = u;
+                    squares += u * u;
+                }
+                if (sum_out) {
+                    float total = 0.0f;
+#pragma unroll
+                    for (int r = 0; r < MAX_COPIES; ++r)
+                        if (r < copies) total += nx[r][e];
+                    sum_out[at + i + e] = total;
+                }
+            }
         }
-    }
+    };
+    if (hidden % 4 == 0) walk(std::integral_constant<int, 4>{});
+    else walk(std::integral_constant<int, 1>{});
     if (!read) return;
     const float scale = rsqrtf(block_sum(squares, scratch) / (float)hidden + eps);
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) normed[at + i] = from_f32<AT>(row_u[i] * scale * norm_w[i]);

@@ -67,7 +67,7 @@ _SIGNATURES = {
     "shiso_store_kv": [P, LL, P, LL, I, P, P, P, I, P, P, I, I, I, I, I, P],
     "shiso_pool_kv": [P, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, P],
     "shiso_pooled_window_attention": [P, LL, I, P, P, P, P, P, P, I, P, P, P, LL, P, I, I, I, I, I, I, F, I, I, F, P],
-    "shiso_prefill_attention_tc_open": [P, LL, P, P, P, I, P, P, P, LL, P, I, I, I, I, I, I, LL, F, I, P],
+    "shiso_prefill_attention_tc_open": [P, LL, P, P, P, I, P, P, P, LL, P, F, I, I, I, I, I, I, LL, F, I, P],
 }
 
 

@@ -1094,7 +1094,7 @@ def pooled_window_attention(q, heads, k_cache, v_cache, block_table, pooled_k, p
         seen = torch.empty((tokens, heads), dtype=torch.float32, device=q.device)
         status = lib.shiso_prefill_attention_tc_open(
             q.data_ptr(), q_ld, _ptr(k_cache), _ptr(v_cache), _ptr(block_table), block_table.shape[1], _ptr(step.q_start),
-            _ptr(step.start_pos), out.data_ptr(), out_ld, _ptr(seen), tokens, step.num_seqs, tiles, heads, kv_heads, page_size,
+            _ptr(step.start_pos), out.data_ptr(), out_ld, _ptr(seen), float(out_scale), tokens, step.num_seqs, tiles, heads, kv_heads, page_size,
             k_cache.shape[0], float(scale), int(window), _stream(),
         )
         _done(status, "prefill_attention (tcgen05, window of pooled_window_attention)", shape=(tokens, heads, dim))
