@@ -75,7 +75,21 @@ DOC_B = {
     ],
 }
 
-DOCS = {"A": (DOC_A, 3), "B": (DOC_B, 4)}
+# sizes that no vector width divides: an odd width and vocabulary, head sizes of 10, 6 and 7, four copies
+DOC_C = {
+    "architecture": "Filulix", "vocab": 333, "width": 50, "streams": 4, "norm": {"eps": 1e-5},
+    "embedding": {"scale": 7.0, "bigram": {"buckets": 50, "mul_prev": 1, "mul_cur": 1}},
+    "layers": [
+        wkv_layer(5, 10, 3, 30),
+        parallel_layer(
+            {"heads": 3, "kv_heads": 3, "dim": 6, "vdim": 7, "scale": 0.5, "mask": {"size": 20, "pool": 3}},
+            {"heads": 3, "dim": 6, "vdim": 9, "decay": [0.75, 0.9375, 0.998], "rot": {"dims": 2, "base": 7.0}},
+            (1.5, 0.75), 22),
+    ],
+    "loop": {"start": 0, "stop": 1, "times": 3},
+}
+
+DOCS = {"A": (DOC_A, 3), "B": (DOC_B, 4), "C": (DOC_C, 5)}
 
 
 def check_rows(got, ref, dtype, what):
@@ -179,7 +193,7 @@ def test_cache_needs_of_composite_mixers_and_pooled_rows():
 
 
 @pytest.mark.parametrize("backend", BACKENDS)
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_every_cut_matches_the_plain_implementation(tmp_path, backend, name):
     doc, seed = DOCS[name]
     tensors = helpers.make_folder(tmp_path, doc, seed, std=0.15)
@@ -259,6 +273,44 @@ def test_long_decoding_through_pages_that_are_given_back(tmp_path, backend):
         check_rows(replay.stack_rows(rows, "a", 230), reference["a"], dtype, f"long decoding {dtype}")
         check_rows(replay.stack_rows(rows, "b", 110), reference["b"], dtype, f"the request that joined {dtype}")
         assert engine.cache.free_pages()[0] == 88 and engine.cache.slots.free_slots == 4
+
+
+DOC_WIDE = {
+    "architecture": "Filulix", "vocab": 400, "width": 128, "streams": 2, "norm": {"eps": 1e-6},
+    "embedding": {"scale": 4.0, "bigram": {"buckets": 211, "mul_prev": 29, "mul_cur": 3}},
+    "layers": [
+        parallel_layer(
+            {"heads": 6, "kv_heads": 3, "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": 200, "pool": 24}},
+            {"heads": 2, "dim": 16, "vdim": 32, "decay": [0.97, 0.999], "rot": {"dims": 16, "base": 10000.0}},
+            (0.8, 0.6), 160),
+        wkv_layer(2, 64, 8, 160),
+    ],
+    "loop": {"start": 0, "stop": 2, "times": 2},
+}
+
+
+@pytest.mark.gpu
+def test_long_bfloat16_portions_take_the_tensor_memory_window(tmp_path):
+    """Heads of 64 in bfloat16: a step with a long portion sends the window's tokens to the
+    tensor-memory attention kernel and folds the pooled blocks in afterwards; shorter portions and
+    decoded tokens take the general kernel.  Both against the plain implementation, whole, in
+    portions on either side of the route's limits, and with a second request in the batch."""
+    tensors = helpers.make_folder(tmp_path, DOC_WIDE, 9, std=0.08)
+    a = helpers.random_prompt(700, DOC_WIDE["vocab"], 1)
+    b = helpers.random_prompt(150, DOC_WIDE["vocab"], 2)
+    reference = {"a": reference_logits(DOC_WIDE, tensors, a), "b": reference_logits(DOC_WIDE, tensors, b)}
+    for dtype in ("bfloat16", "float32"):
+        engine = helpers.make_engine(tmp_path, dtype, page_size=16, kv_cache_tokens=2048, ctx=1024, max_num_batched_tokens=1024)
+        rows = helpers.run_steps(engine, helpers.whole("w", a))
+        check_rows(replay.stack_rows(rows, "w", 700), reference["a"], dtype, f"one long portion {dtype}")
+        rows = helpers.run_steps(engine, helpers.portions("p", a, [300, 100, 260, 1, 39]))
+        check_rows(replay.stack_rows(rows, "p", 700), reference["a"], dtype, f"long and short portions {dtype}")
+        steps = [([("a", a[:400], list(range(400))), ("b", b[:5], list(range(5)))], []),
+                 ([("b", b[5:6], [0]), ("a", a[400:], list(range(300)))], ["a"]),
+                 ([("b", b[6:], list(range(144)))], ["b"])]
+        rows = helpers.run_steps(engine, steps)
+        check_rows(replay.stack_rows(rows, "a", 700), reference["a"], dtype, f"a long portion in a batch {dtype}")
+        check_rows(replay.stack_rows(rows, "b", 150), reference["b"], dtype, f"its neighbour {dtype}")
 
 
 @pytest.mark.parametrize("backend", BACKENDS)
