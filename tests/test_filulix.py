@@ -313,6 +313,32 @@ def test_long_bfloat16_portions_take_the_tensor_memory_window(tmp_path):
         check_rows(replay.stack_rows(rows, "b", 150), reference["b"], dtype, f"its neighbour {dtype}")
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_through_the_trace_runner(tmp_path, dtype):
+    """``bin/trace_run`` in a process of its own over a pool that holds barely the live requests:
+    whole, last tokens one by one, changing portions and a mixed trace, against the plain logits."""
+    doc, seed = DOCS["A"]
+    model_dir = tmp_path / "model"
+    tensors = helpers.make_folder(model_dir, doc, seed, std=0.15)
+    lengths = [70, 100, 40, 7, 33, 1]
+    requests = {f"r{i}": helpers.random_prompt(n, doc["vocab"], 60 + i) for i, n in enumerate(lengths)}
+    steps, expect = [], []
+    for rid, toks in requests.items():
+        steps += helpers.whole(f"w-{rid}", toks)
+        expect.append((f"w-{rid}", rid))
+    steps += helpers.tail_one_by_one("t-r1", requests["r1"], 32)
+    steps += helpers.portions("p-r1", requests["r1"], [13, 2, 7, 64, 3])
+    steps += helpers.portions("p-r0", requests["r0"], [2, 3, 1, 2, 5, 1, 1, 17])
+    expect += [("t-r1", "r1"), ("p-r1", "r1"), ("p-r0", "r0")]
+    steps += replay.mixed_trace({f"m-{k}": v for k, v in requests.items()}, 5, 320)
+    expect += [(f"m-{rid}", rid) for rid in requests]
+    rows = replay.run_trace_run(model_dir, dtype, steps, 320, tmp_path / "out", doc["vocab"])
+    for trace_id, rid in expect:
+        got = replay.stack_rows(rows, trace_id, len(requests[rid]))
+        check_rows(got, reference_logits(doc, tensors, requests[rid]), dtype, f"{dtype} {trace_id}")
+
+
 @pytest.mark.parametrize("backend", BACKENDS)
 def test_greedy_generation_through_the_scheduler(tmp_path, backend):
     doc, seed = DOCS["B"]
