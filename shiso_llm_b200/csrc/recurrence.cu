@@ -43,6 +43,10 @@ struct RecurrenceArgs {
     const float* out_weight;
     float eps, out_scale;
     int heads, dim, vdim;
+    // With `raw` (float [T, heads * vdim]) a head's value columns are shared out over col_parts CTAs
+    // (blockIdx.z), which leave the unnormalised outputs there; unit RMS, weight and gate follow in
+    // a row kernel.  For long portions: more SMs walk the same tokens, each with fewer columns.
+    float* raw; int col_parts;
 };
 
 // Threads a CTA may have so that RPT rows of the state (and what else a thread needs) stay in registers.
@@ -58,10 +62,12 @@ __global__ void __launch_bounds__(rec_max_threads(RPT)) decay_recurrence_kernel(
     __shared__ float red[REC_BATCH][32];
     const int head = blockIdx.x, seq = blockIdx.y;
     const int tid = threadIdx.x, threads = blockDim.x;
-    const int j = tid / SPLIT, part = tid % SPLIT;
+    const int part = tid % SPLIT;
     const int dim = a.dim, vdim = a.vdim;
+    const int cols = vdim / a.col_parts;  // value columns of this CTA
+    const int j = blockIdx.z * cols + tid / SPLIT;  // this thread's column
     const int rpt = dim / SPLIT;  // rows of the state per thread (dim is a multiple of SPLIT)
-    const bool owns = j < vdim;
+    const bool owns = tid / SPLIT < cols;
     const int lane = tid & 31, warp = tid >> 5, nwarps = (threads + 31) >> 5;
     // tokens per batch: what the threads can stage with REC_STAGED channels each (at least two:
     // the CTA has half as many threads as there are key channels)
@@ -211,11 +217,15 @@ __global__ void __launch_bounds__(rec_max_threads(RPT)) decay_recurrence_kernel(
         for (int i = 0; i < REC_BATCH; ++i) {
 #pragma unroll
             for (int off = 1; off < SPLIT; off <<= 1) o[i] += __shfl_xor_sync(0xffffffffu, o[i], off);
-            const float partial = warp_sum((owns && part == 0) ? o[i] * o[i] : 0.0f);
-            if (lane == 0) red[i][warp] = partial;
+            if (a.raw) {
+                if (owns && i % SPLIT == part && i < n) a.raw[(size_t)(t0 + i) * a.heads * vdim + (size_t)head * vdim + j] = o[i];
+            } else {
+                const float partial = warp_sum((owns && part == 0) ? o[i] * o[i] : 0.0f);
+                if (lane == 0) red[i][warp] = partial;
+            }
         }
         __syncthreads();  // every thread has read the staged batch; the sums of squares are written
-        if (owns) {
+        if (owns && !a.raw) {
             // (every lane of a column holds the column's sums: the lanes share the batch's tokens)
 #pragma unroll
             for (int i = 0; i < REC_BATCH; ++i) {
@@ -245,9 +255,9 @@ template <typename AT, int SPLIT, bool CHANNEL>
 static int launch_recurrence(const RecurrenceArgs& a, int num_seqs, cudaStream_t stream) {
     const int rpt = a.dim / SPLIT;
     // a thread per lane of a column, and at least half as many threads as key channels (they stage q and k)
-    const int columns = (a.vdim * SPLIT + 31) / 32 * 32, stagers = ((a.dim + 1) / 2 + 31) / 32 * 32;
+    const int columns = (a.vdim / a.col_parts * SPLIT + 31) / 32 * 32, stagers = ((a.dim + 1) / 2 + 31) / 32 * 32;
     const unsigned threads = (unsigned)(columns > stagers ? columns : stagers);
-    const dim3 grid(a.heads, num_seqs);
+    const dim3 grid(a.heads, num_seqs, a.col_parts);
 #define SHISO_REC(R)                                                                                          \
     if constexpr (R * SPLIT <= REC_MAX_DIM) {                                                                 \
         if (rpt <= R) {                                                                                       \
@@ -284,7 +294,7 @@ SHISO_API int shiso_decay_recurrence_supported(int dim, int vdim) {
 
 template <typename AT, bool CHANNEL>
 static int pick_split(const RecurrenceArgs& a, int num_seqs, cudaStream_t stream) {
-    switch (choose_split(a.dim, a.vdim)) {
+    switch (choose_split(a.dim, a.vdim / a.col_parts)) {
         case 8: return launch_recurrence<AT, 8, CHANNEL>(a, num_seqs, stream);
         case 4: return launch_recurrence<AT, 4, CHANNEL>(a, num_seqs, stream);
         case 2: return launch_recurrence<AT, 2, CHANNEL>(a, num_seqs, stream);
@@ -293,13 +303,49 @@ static int pick_split(const RecurrenceArgs& a, int num_seqs, cudaStream_t stream
     return SHISO_ERR_SHAPE;
 }
 
+// Unit RMS over a head's value channels, times weight, silu(gate) and a constant: what follows the
+// recurrence when its outputs were left unnormalised.  A warp per (row, head).
+template <typename AT>
+__global__ void unit_rms_gate_kernel(const float* __restrict__ raw, const AT* __restrict__ gate, long long gate_ld,
+                                     const float* __restrict__ out_weight, AT* __restrict__ out, long long out_ld, int tokens,
+                                     int heads, int vdim, float eps, float out_scale) {
+    pdl_begin();
+    const int lane = threadIdx.x & 31;
+    const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (item >= (long long)tokens * heads) return;
+    const int t = (int)(item / heads), head = (int)(item % heads);
+    const float* o = raw + ((size_t)t * heads + head) * vdim;
+    float vals[REC_MAX_DIM / 32];
+    float squares = 0.0f;
+#pragma unroll
+    for (int e = 0; e < REC_MAX_DIM / 32; ++e) {
+        const int c = e * 32 + lane;
+        vals[e] = c < vdim ? o[c] : 0.0f;
+        squares += vals[e] * vals[e];
+    }
+    const float unit = rsqrtf(warp_sum(squares) / (float)vdim + eps);
+#pragma unroll
+    for (int e = 0; e < REC_MAX_DIM / 32; ++e) {
+        const int c = e * 32 + lane;
+        if (c < vdim) {
+            float y = vals[e] * unit;
+            if (out_weight) y *= out_weight[head * vdim + c];
+            if (gate) {
+                const float g = to_f32(gate[(size_t)t * gate_ld + (size_t)head * vdim + c]);
+                y *= g / (1.0f + expf(-g));
+            }
+            out[(size_t)t * out_ld + (size_t)head * vdim + c] = from_f32<AT>(y * out_scale);
+        }
+    }
+}
+
 SHISO_API int shiso_decay_recurrence(const void* q, const void* k, const void* v, const void* gate, long long q_ld, long long k_ld,
                                      long long v_ld, long long gate_ld, void* out, long long out_ld, int act_dtype, float* state,
                                      long long state_stride, const int* q_start, const int* slots, const int* positions,
                                      const float* decay_logits, long long logits_ld, const float* decay_bias, const float* bonus,
                                      const float* head_loss, const float* inv_freq, int rotary_dim, float key_scale,
-                                     const float* out_weight, float eps, float out_scale, int num_seqs, int heads, int dim,
-                                     int vdim, cudaStream_t stream) {
+                                     const float* out_weight, float eps, float out_scale, float* raw, int col_parts, int tokens,
+                                     int num_seqs, int heads, int dim, int vdim, cudaStream_t stream) {
     if (num_seqs <= 0 || heads <= 0) return SHISO_OK;
     if (dim <= 0 || vdim <= 0 || dim > REC_MAX_DIM || vdim > REC_MAX_DIM || dim * vdim > REC_MAX_STATE) return SHISO_ERR_SHAPE;
     const bool channel = decay_logits != nullptr;
@@ -315,8 +361,20 @@ SHISO_API int shiso_decay_recurrence(const void* q, const void* k, const void* v
     a.head_loss = head_loss; a.inv_freq = inv_freq; a.rotary_dim = rotary_dim; a.key_scale = key_scale;
     a.out_weight = out_weight; a.eps = eps; a.out_scale = out_scale;
     a.heads = heads; a.dim = dim; a.vdim = vdim;
-    if (act_dtype == SHISO_F32) return channel ? pick_split<float, true>(a, num_seqs, stream) : pick_split<float, false>(a, num_seqs, stream);
-    if (act_dtype == SHISO_BF16)
-        return channel ? pick_split<__nv_bfloat16, true>(a, num_seqs, stream) : pick_split<__nv_bfloat16, false>(a, num_seqs, stream);
-    return SHISO_ERR_DTYPE;
+    a.raw = raw; a.col_parts = raw ? col_parts : 1;
+    if (a.col_parts < 1 || vdim % a.col_parts || !shiso_decay_recurrence_supported(dim, vdim / a.col_parts)) return SHISO_ERR_SHAPE;
+    int status;
+    if (act_dtype == SHISO_F32) status = channel ? pick_split<float, true>(a, num_seqs, stream) : pick_split<float, false>(a, num_seqs, stream);
+    else if (act_dtype == SHISO_BF16)
+        status = channel ? pick_split<__nv_bfloat16, true>(a, num_seqs, stream) : pick_split<__nv_bfloat16, false>(a, num_seqs, stream);
+    else return SHISO_ERR_DTYPE;
+    if (status != SHISO_OK || !raw) return status;
+    const unsigned blocks = ceil_div_u((long long)tokens * heads, 8);
+    if (act_dtype == SHISO_F32)
+        launch_kernel(unit_rms_gate_kernel<float>, blocks, 256, 0, stream, (const float*)raw, (const float*)gate, gate_ld, out_weight,
+                      (float*)out, out_ld, tokens, heads, vdim, eps, out_scale);
+    else
+        launch_kernel(unit_rms_gate_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const float*)raw, (const __nv_bfloat16*)gate, gate_ld,
+                      out_weight, (__nv_bfloat16*)out, out_ld, tokens, heads, vdim, eps, out_scale);
+    return launch_status();
 }

@@ -63,7 +63,7 @@ _SIGNATURES = {
     "shiso_token_shift_blend": [P, I, P, P, LL, P, P, P, P, P, I, I, I, I, P],
     "shiso_unary": [P, I, P, I, LL, I, P],
     "shiso_decay_recurrence_supported": [I, I],
-    "shiso_decay_recurrence": [P, P, P, P, LL, LL, LL, LL, P, LL, I, P, LL, P, P, P, P, LL, P, P, P, P, I, F, P, F, F, I, I, I, I, P],
+    "shiso_decay_recurrence": [P, P, P, P, LL, LL, LL, LL, P, LL, I, P, LL, P, P, P, P, LL, P, P, P, P, I, F, P, F, F, P, I, I, I, I, I, I, P],
     "shiso_store_kv": [P, LL, P, LL, I, P, P, P, I, P, P, I, I, I, I, I, P],
     "shiso_pool_kv": [P, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, P],
     "shiso_pooled_window_attention": [P, LL, I, P, P, P, P, P, P, I, P, P, P, LL, P, I, I, I, I, I, I, F, I, I, F, P],

@@ -954,6 +954,9 @@ def _rows(t, name, dtype, width=None) -> int:
     return t.stride(0)
 
 
+RECURRENCE_SPLIT_MIN_PORTION = 64  # portions from here on may share a head's value columns out over several CTAs
+
+
 def recurrence_supported(dim: int, vdim: int) -> bool:
     return bool(library().shiso_decay_recurrence_supported(int(dim), int(vdim)))
 
@@ -1001,14 +1004,25 @@ def decay_recurrence(q, k, v, out, state, step, heads, dim, vdim, eps, *, decay_
         _check(out_weight, "output weight", torch.float32, 1)
         if out_weight.shape[0] != heads * vdim:
             raise KernelError(f"an output weight of {out_weight.shape[0]} for {heads} heads of {vdim}")
+    # Long portions: a head's value columns are shared out over several CTAs (few heads and sequences
+    # would leave most SMs idle while one walks thousands of tokens); the outputs' unit RMS, weight
+    # and gate then follow in a row kernel.  The split depends on the step's shape only.
+    col_parts, raw = 1, None
+    if not getattr(step, "all_decode", False) and getattr(step, "max_q_len", tokens) >= RECURRENCE_SPLIT_MIN_PORTION:
+        while (col_parts < 8 and heads * step.num_seqs * col_parts < _sm_count() and vdim % (2 * col_parts) == 0
+               and vdim // (2 * col_parts) >= 8 and recurrence_supported(dim, vdim // (2 * col_parts))):
+            col_parts *= 2
+        if col_parts > 1:
+            raw = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=q.device)
     status = library().shiso_decay_recurrence(
         q.data_ptr(), k.data_ptr(), v.data_ptr(), gate.data_ptr() if gate is not None else 0, q_ld, k_ld, v_ld, gate_ld,
         out.data_ptr(), out_ld, _CODES[act], state.data_ptr(), stride, _ptr(step.q_start), _ptr(step.state_slots),
         _ptr(step.positions), _ptr(decay_logits), logits_ld, _ptr(decay_bias), _ptr(bonus), _ptr(head_loss),
         _ptr(inv_freq) if rotary_dim else 0, int(rotary_dim), float(key_scale), _ptr(out_weight), float(eps), float(out_scale),
-        step.num_seqs, heads, dim, vdim, _stream(),
+        _ptr(raw), col_parts, tokens, step.num_seqs, heads, dim, vdim, _stream(),
     )
-    _done(status, "decay_recurrence", shape=(tokens, heads, dim, vdim))
+    _done(status, "decay_recurrence" + (f" (columns over {col_parts} CTAs)" if raw is not None else ""), 2 if raw is not None else 1,
+          shape=(tokens, heads, dim, vdim))
     return out
 
 
