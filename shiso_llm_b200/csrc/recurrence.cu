@@ -116,25 +116,37 @@ __global__ void __launch_bounds__(rec_max_threads(RPT)) decay_recurrence_kernel(
     // What a batch of tokens brings is asked for one batch ahead: the loads are in flight while the
     // state walks the batch before.
     struct Raw { float q[REC_STAGED], k[REC_STAGED], q_other[REC_STAGED], k_other[REC_STAGED], v[REC_BATCH]; };
+    // (Every load below has a valid address whatever n is - a token index beyond the batch is the
+    // batch's last, an idle thread's column is the CTA's first - and nothing is converted before all
+    // are asked for: a branch or a conversion between two loads would make each wait for the one before.)
+    const int jc = owns ? j : blockIdx.z * cols;
     auto fetch = [&](int t0, int n, Raw& r) {
+        AT raw_q[REC_STAGED], raw_k[REC_STAGED], raw_qo[REC_STAGED], raw_ko[REC_STAGED], raw_v[REC_BATCH];
+        float raw_logit[REC_STAGED];
 #pragma unroll
         for (int l = 0; l < REC_STAGED; ++l) {
-            r.q[l] = r.k[l] = r.q_other[l] = r.k_other[l] = 0.0f;
-            if (st_token[l] < n) {
-                const int t = t0 + st_token[l], c = st_chan[l];
-                r.q[l] = to_f32(q[(size_t)t * a.q_ld + c]);
-                r.k[l] = to_f32(k[(size_t)t * a.k_ld + c]);
-                if (CHANNEL) {
-                    r.q_other[l] = a.decay_logits[(size_t)t * a.logits_ld + head * dim + c];
-                } else if (c < a.rotary_dim) {
-                    const int other = c < half ? c + half : c - half;
-                    r.q_other[l] = to_f32(q[(size_t)t * a.q_ld + other]);
-                    r.k_other[l] = to_f32(k[(size_t)t * a.k_ld + other]);
-                }
+            const int t = t0 + min(st_token[l], n - 1), c = st_chan[l];
+            raw_q[l] = q[(size_t)t * a.q_ld + c];
+            raw_k[l] = k[(size_t)t * a.k_ld + c];
+            if (CHANNEL) {
+                raw_logit[l] = a.decay_logits[(size_t)t * a.logits_ld + head * dim + c];
+            } else {
+                const int other = c < a.rotary_dim ? (c < half ? c + half : c - half) : c;
+                raw_qo[l] = q[(size_t)t * a.q_ld + other];
+                raw_ko[l] = k[(size_t)t * a.k_ld + other];
             }
         }
 #pragma unroll
-        for (int i = 0; i < REC_BATCH; ++i) r.v[i] = (owns && i < n) ? to_f32(v[(size_t)(t0 + i) * a.v_ld + j]) : 0.0f;
+        for (int i = 0; i < REC_BATCH; ++i) raw_v[i] = v[(size_t)(t0 + min(i, n - 1)) * a.v_ld + jc];
+#pragma unroll
+        for (int l = 0; l < REC_STAGED; ++l) {
+            r.q[l] = to_f32(raw_q[l]);
+            r.k[l] = to_f32(raw_k[l]);
+            r.q_other[l] = CHANNEL ? raw_logit[l] : to_f32(raw_qo[l]);
+            r.k_other[l] = CHANNEL ? 0.0f : to_f32(raw_ko[l]);
+        }
+#pragma unroll
+        for (int i = 0; i < REC_BATCH; ++i) r.v[i] = to_f32(raw_v[i]);
     };
     auto stage = [&](int t0, int n, const Raw& r) {
 #pragma unroll
@@ -176,9 +188,16 @@ __global__ void __launch_bounds__(rec_max_threads(RPT)) decay_recurrence_kernel(
         const int n_next = min(batch, last - t0 - n);
         if (n_next > 0) fetch(t0 + n, n_next, next);
         float gates[REC_BATCH];  // asked for now, needed after the batch is walked
+        if (gate && !a.raw) {
+            AT raw_gate[REC_BATCH];
 #pragma unroll
-        for (int i = 0; i < REC_BATCH; ++i)
-            gates[i] = (gate && owns && i % SPLIT == part && i < n) ? to_f32(gate[(size_t)(t0 + i) * a.gate_ld + j]) : 0.0f;
+            for (int i = 0; i < REC_BATCH; ++i) raw_gate[i] = gate[(size_t)(t0 + min(i, n - 1)) * a.gate_ld + jc];
+#pragma unroll
+            for (int i = 0; i < REC_BATCH; ++i) gates[i] = to_f32(raw_gate[i]);
+        } else {
+#pragma unroll
+            for (int i = 0; i < REC_BATCH; ++i) gates[i] = 0.0f;
+        }
         __syncthreads();  // the batch is staged
         float o[REC_BATCH];
 #pragma unroll
