@@ -179,25 +179,26 @@ __device__ __forceinline__ void fold_chunk(const CT* __restrict__ k_cache, const
     run_weight[lane] = weight;
     run_row[lane] = row >= 0 ? ((long long)row * kv_heads + kv_head) * vdim : -1;
     __syncwarp();
-    // (unrolled, so that the value rows of eight keys are asked for together)
+    // (unrolled and without a branch between two loads - a key the run does not have reads row 0 with
+    // weight zero - so that the value rows of eight keys are asked for together)
 #pragma unroll 8
     for (int kk = 0; kk < 32; ++kk) {
         const long long r = run_row[kk];
-        if (r < 0) continue;  // also every lane beyond the run's keys
-        const float w = run_weight[kk];
-        const CT* value = v_cache + r;
+        const bool live = r >= 0;
+        const float w = live ? run_weight[kk] : 0.0f;
+        const CT* value = v_cache + (live ? r : 0);
 #pragma unroll
         for (int e = 0; e < PWA_PAIRS; ++e) {
             const int c = e * 64 + 2 * lane;
             if (paired) {
                 if (c < vdim) {
                     const float2 v2 = load_pair(value + c);
-                    acc[e][0] += w * v2.x;
-                    acc[e][1] += w * v2.y;
+                    acc[e][0] += live ? w * v2.x : 0.0f;
+                    acc[e][1] += live ? w * v2.y : 0.0f;
                 }
             } else {
-                if (c < vdim) acc[e][0] += w * to_f32(value[c]);
-                if (c + 1 < vdim) acc[e][1] += w * to_f32(value[c + 1]);
+                if (c < vdim) acc[e][0] += live ? w * to_f32(value[c]) : 0.0f;
+                if (c + 1 < vdim) acc[e][1] += live ? w * to_f32(value[c + 1]) : 0.0f;
             }
         }
     }
