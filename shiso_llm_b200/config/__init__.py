@@ -13,7 +13,9 @@ from .registry import (
 )
 from . import lfm2  # registers Lfm2ForCausalLM
 from . import filulix  # registers Filulix
+from . import zetavik  # registers Zetavik
 from .filulix import FilulixConfig
+from .zetavik import ZetavikConfig
 from .lfm2 import Lfm2Config, feed_forward_width
 
 __all__ = [
@@ -25,6 +27,7 @@ __all__ = [
     "Lfm2Config",
     "UnknownArchitecture",
     "UnsupportedShape",
+    "ZetavikConfig",
     "architecture_of",
     "feed_forward_width",
     "load_config",

@@ -258,7 +258,8 @@ class Stream:
     """The residual stream between blocks.
 
     ``residual`` is float32 ``[T, hidden]``.  ``pending`` is a block output not yet
-    added: the next norm adds it while it normalises (one fused kernel), which is how
+    added (or a tuple of them, from a layer whose sublayers run side by side): the next norm
+    adds it while it normalises (one fused kernel), which is how
     the reference closes every block (crates/shiso-engine/src/layers.rs:2476-2498)."""
 
     def __init__(self, residual: torch.Tensor, observer: Optional[Callable] = None):
@@ -305,6 +306,10 @@ class Stream:
         if self.pending is None:
             return norm.apply(self.residual)
         delta, self.pending = self.pending, None
+        if isinstance(delta, tuple):
+            if not getattr(norm, "takes_several", False):
+                raise RuntimeError(f"{type(norm).__name__} adds one block output at a time, {len(delta)} are waiting")
+            return norm.add_apply(self.residual, tuple(d.materialize() if isinstance(d, DeferredLinear) else d for d in delta))
         if isinstance(delta, DeferredLinear):
             fused = getattr(norm, "add_apply_linear", None)
             if fused is not None:
@@ -313,8 +318,11 @@ class Stream:
         return norm.add_apply(self.residual, delta)
 
     def take_pending(self) -> Optional[torch.Tensor]:
-        """The block output still waiting to be added, as a tensor (or None)."""
+        """The block output still waiting to be added, as a tensor (or None); a tuple of tensors
+        where a layer left several."""
         delta, self.pending = self.pending, None
+        if isinstance(delta, tuple):
+            return tuple(d.materialize() if isinstance(d, DeferredLinear) else d for d in delta)
         if isinstance(delta, DeferredLinear):
             delta = delta.materialize()
         return delta

@@ -46,3 +46,43 @@ class PreNormBlock(Block):
         if self.feed_forward is not None:
             x = stream.normed(self.ff_norm, getattr(self.feed_forward, "takes_deferred_norm", False))
             stream.add(self.feed_forward.forward(x, step))
+
+
+@BLOCKS.register("parallel_pre_norm")
+class ParallelPreNormBlock(Block):
+    """``x' = x + mixer(h) + ff(h)`` with ``h = norm(x)``: one norm, read by both sublayers.
+    Both outputs wait on the stream together; the next norm adds them in float32 while it
+    normalises.  A layer without a feed-forward leaves the mixer's output alone."""
+
+    def __init__(self, spec, env, layer):
+        super().__init__(spec, env)
+        self.name = layer.name
+        if layer.feed_forward_norm is not None:
+            raise ValueError(f"layer {layer.name}: a parallel layer has one norm, read by the mixer and the feed-forward")
+        self.norm = NORMS.build(layer.mixer_norm, env)
+        self.mixer = MIXERS.build(layer.mixer, env)
+        self.feed_forward = FEED_FORWARDS.build(layer.feed_forward, env) if layer.feed_forward is not None else None
+
+    def sub_parts(self):
+        return [p for p in (self.norm, self.mixer, self.feed_forward) if p is not None]
+
+    def tensor_specs(self):
+        specs = []
+        for part in self.sub_parts():
+            specs += part.tensor_specs()
+        return specs
+
+    def bind(self, tensors):
+        for part in self.sub_parts():
+            part.bind(tensors)
+
+    def mixer_part(self):
+        return self.mixer
+
+    def forward(self, stream, step, cache):
+        h = stream.normed(self.norm)
+        mixed = self.mixer.forward(h, step, cache)
+        if self.feed_forward is None:
+            stream.add(mixed)
+        else:
+            stream.add((mixed, self.feed_forward.forward(h, step)))

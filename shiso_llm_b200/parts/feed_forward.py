@@ -5,14 +5,21 @@ projection (crates/shiso-engine/src/ffn.rs:234-239); here they are joined into o
 ``[2I, H]`` matrix when bound, so one product yields ``[gate | up]`` rows; the activation
 (kernels/cuda/generic/glu.cuh:35-57: alpha 1, no clamp) is applied in the product's epilogue
 for decode-sized batches and by a kernel of its own otherwise.
+
+``relu2_ff`` is ``W_down relu(W_up x)^2``; ``routed_experts`` a mixture of gated experts
+behind a router with group-limited choice (see the classes).
 """
 
 from __future__ import annotations
 
 import torch
 
+from ..config.errors import UnsupportedShape
 from ..weights.spec import TensorSpec
 from .base import FEED_FORWARDS, DeferredLinear, FeedForward, project
+
+MAX_EXPERTS = 256  # what the routing kernel keeps of a token's scores in a warp's registers ...
+MAX_TOP = 16  # ... and how many choices it makes per token
 
 
 @FEED_FORWARDS.register("swiglu")
@@ -48,3 +55,107 @@ class SwiGLU(FeedForward):
         ops = self.env.ops
         mid = project(ops, x, self.gate_up, self.env.dtype, glu=True)
         return DeferredLinear(ops, mid, self.down, self.env.dtype)
+
+
+@FEED_FORWARDS.register("relu2_ff")
+class Relu2FeedForward(FeedForward):
+    """``W_down relu(W_up x)^2``; names ``up`` and ``down``."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.inter = int(p["intermediate_size"])
+        self.names = (p["up"], p["down"])
+        self.up = self.down = None
+
+    def tensor_specs(self):
+        up, down = self.names
+        return [TensorSpec(up, (self.inter, self.hidden)), TensorSpec(down, (self.hidden, self.inter))]
+
+    def bind(self, tensors):
+        self.up, self.down = tensors[self.names[0]], tensors[self.names[1]]
+
+    def forward(self, x, step):
+        ops = self.env.ops
+        mid = ops.unary(project(ops, x, self.up, self.env.dtype), "relu2", self.env.dtype)
+        return DeferredLinear(ops, mid, self.down, self.env.dtype)
+
+
+@FEED_FORWARDS.register("routed_experts")
+class RoutedExperts(FeedForward):
+    """A mixture of gated experts ``W_down (silu(W_gate x) * (W_up x))``, ``top`` of ``experts``
+    per token, plus an optional feed-forward that every token runs (``shared``, a PartSpec).
+
+    Router: logits ``W_router x`` in float32; scores are their softmax over all experts
+    (``scores = "softmax"``) or their sigmoids (``"sigmoid"``).  Experts form ``group_count``
+    equal groups of neighbours; a group's score is its largest score, and only experts of the
+    ``group_keep`` best groups can be chosen (one group of all experts: no limit).  The ``top``
+    largest scores among those win (the lower index on a tie); a token's weights are the
+    chosen scores - divided by their sum with ``renormalize`` - times ``scale``.
+
+    The expert matrices are stacked ``[experts, 2 ff, hidden]`` (gate over up) and
+    ``[experts, hidden, ff]`` when bound; a step's (token, choice) pairs are grouped by expert
+    on the device and each group runs as row tiles of one launch, so nothing about the routing
+    reaches the host and a captured step can be replayed."""
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        p = spec.params
+        self.hidden = int(p["hidden_size"])
+        self.inter = int(p["intermediate_size"])
+        self.experts = int(p["experts"])
+        self.top = int(p["top"])
+        self.group_count = int(p.get("group_count", 1))
+        self.group_keep = int(p.get("group_keep", self.group_count))
+        self.scale = float(p.get("scale", 1.0))
+        self.scores = p.get("scores", "softmax")
+        self.renormalize = bool(p.get("renormalize", False))
+        if self.scores not in ("softmax", "sigmoid"):
+            raise UnsupportedShape("router scores", self.scores, "expected 'softmax' or 'sigmoid'")
+        if not 0 < self.top <= self.experts or self.experts % self.group_count or not 0 < self.group_keep <= self.group_count:
+            raise UnsupportedShape("router", (self.experts, self.top, self.group_count, self.group_keep), "top <= experts, groups must divide the experts, keep <= groups")
+        if self.group_keep * (self.experts // self.group_count) < self.top:
+            raise UnsupportedShape("router groups", (self.group_count, self.group_keep), f"the kept groups hold fewer than {self.top} experts")
+        if self.experts > MAX_EXPERTS or self.top > MAX_TOP:
+            raise UnsupportedShape("router", (self.experts, self.top), f"the routing kernel takes up to {MAX_EXPERTS} experts and {MAX_TOP} choices")
+        self.router_name = p["router"]
+        self.expert_names = tuple(p["expert_names"])
+        if len(self.expert_names) != self.experts:
+            raise ValueError(f"{len(self.expert_names)} sets of names for {self.experts} experts")
+        self.shared = FEED_FORWARDS.build(p["shared"], env) if p.get("shared") is not None else None
+        self.router = self.gate_up = self.down = None
+
+    def sub_parts(self):
+        return [self.shared] if self.shared is not None else []
+
+    def tensor_specs(self):
+        specs = [TensorSpec(self.router_name, (self.experts, self.hidden))]
+        for names in self.expert_names:
+            specs += [TensorSpec(names["gate"], (self.inter, self.hidden)), TensorSpec(names["up"], (self.inter, self.hidden)),
+                      TensorSpec(names["down"], (self.hidden, self.inter))]
+        if self.shared is not None:
+            specs += self.shared.tensor_specs()
+        return specs
+
+    def bind(self, tensors):
+        self.router = tensors[self.router_name]
+        mats = [tensors[n[k]] for n in self.expert_names for k in ("gate", "up", "down")]
+        wide = len({m.dtype for m in mats}) > 1
+        pick = (lambda m: m.float()) if wide else (lambda m: m)
+        self.gate_up = torch.stack([torch.cat([pick(tensors[n["gate"]]), pick(tensors[n["up"]])], dim=0) for n in self.expert_names]).contiguous()
+        self.down = torch.stack([pick(tensors[n["down"]]) for n in self.expert_names]).contiguous()
+        if self.shared is not None:
+            self.shared.bind(tensors)
+
+    def forward(self, x, step):
+        ops = self.env.ops
+        logits = ops.linear(x, self.router, torch.float32)
+        ids, weights = ops.moe_route(logits, self.top, self.group_count, self.group_keep, self.scale,
+                                     self.scores == "sigmoid", self.renormalize)
+        extra = None
+        if self.shared is not None:
+            extra = self.shared.forward(x, step)
+            if isinstance(extra, DeferredLinear):
+                extra = extra.materialize()
+        return ops.routed_experts(x, ids, weights, self.gate_up, self.down, extra)

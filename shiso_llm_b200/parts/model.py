@@ -27,9 +27,12 @@ def stream_value(stream: Stream) -> torch.Tensor:
     waiting = stream.pending
     if waiting is None:
         return x.clone()
-    if isinstance(waiting, DeferredLinear):
-        waiting = waiting.materialize()
-    return x + waiting.to(x.dtype)
+    total = x.clone()
+    for part in waiting if isinstance(waiting, tuple) else (waiting,):
+        if isinstance(part, DeferredLinear):
+            part = part.materialize()
+        total += part.to(x.dtype)
+    return total
 
 
 def residual_stats(label: str, x: torch.Tensor) -> str:

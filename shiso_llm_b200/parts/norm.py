@@ -52,3 +52,33 @@ class RMSNorm(Norm):
         """``residual += deferred.x @ deferred.w^T`` and the norm of the sum, fused where the
         kernel table can (decode-sized bfloat16 steps)."""
         return self.env.ops.linear_add_rmsnorm(deferred.x, deferred.w, residual, self.weight, self.eps, self.env.dtype)
+
+
+@NORMS.register("layernorm")
+class LayerNorm(Norm):
+    """``y = (x - mean) / sqrt(var + eps) * w`` with a weight and no bias; the variance is the
+    mean of the squared deviations; statistics in float32.  ``add_apply`` takes one block
+    output or a tuple of them (a layer whose mixer and feed-forward read the same rows leaves
+    two): they are added to the residual in float32 by the kernel that normalises."""
+
+    takes_several = True
+
+    def __init__(self, spec, env):
+        super().__init__(spec, env)
+        self.tensor_name = spec.params["tensor"]
+        self.size = int(spec.params["size"])
+        self.eps = float(spec.params["eps"])
+        self.weight = None
+
+    def tensor_specs(self):
+        return [TensorSpec(self.tensor_name, (self.size,), VECTOR, ONES)]
+
+    def bind(self, tensors):
+        self.weight = tensors[self.tensor_name]
+
+    def apply(self, x):
+        return self.env.ops.add_layernorm(x, (), self.weight, self.eps, self.env.dtype, None)
+
+    def add_apply(self, residual, delta, rows=None):
+        deltas = tuple(delta) if isinstance(delta, (tuple, list)) else (delta,)
+        return self.env.ops.add_layernorm(residual, deltas, self.weight, self.eps, self.env.dtype, rows)

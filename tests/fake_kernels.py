@@ -319,6 +319,8 @@ def unary(x, kind, out_dtype):
         return torch.tanh(x64).to(out_dtype)
     if kind == "silu":
         return (x64 / (1.0 + torch.exp(-x64))).to(out_dtype)
+    if kind == "relu2":
+        return (torch.relu(x64) ** 2).to(out_dtype)
     raise ValueError(kind)
 
 
@@ -423,3 +425,205 @@ def pooled_window_attention(q, heads, k_cache, v_cache, block_table, pooled_k, p
             res[t, h] = p @ values[:, g]
     out.copy_((res.reshape(T, heads * dv) * out_scale).to(out.dtype))
     return out
+
+
+# --------------------------------------------------------------------------- layer norm, parallel layers
+
+
+def add_layernorm(residual, deltas, w, eps, out_dtype, rows=None):
+    """``residual`` plus every tensor of ``deltas`` (summed in place without ``rows``), then
+    ``(x - mean) / sqrt(var + eps) * w``."""
+    if rows is None:
+        for d in deltas:
+            residual += d.to(residual.dtype)
+        x = residual.to(F64)
+    else:
+        idx = rows.long()
+        x = residual[idx].clone()
+        for d in deltas:
+            x = x + d[idx].to(residual.dtype)
+        x = x.to(F64)
+    dev = x - x.mean(-1, keepdim=True)
+    return (dev / torch.sqrt((dev * dev).mean(-1, keepdim=True) + eps) * w.to(F64)).to(out_dtype)
+
+
+# --------------------------------------------------------------------------- causal convolution, scalar-decay recurrences
+
+
+def _sigmoid(x):
+    return 1.0 / (1.0 + torch.exp(-x))
+
+
+def causal_conv(x, taps, bias, state, step, silu=True):
+    """``y_t[c] = bias[c] + sum_j taps[c, j] x_{t-(L-1)+j}[c]`` per sequence, then silu; the state
+    of each sequence's slot holds its last ``L - 1`` inputs (float32) and is updated."""
+    T, C = x.shape
+    L = taps.shape[1]
+    x64 = x.to(F64)
+    y = torch.zeros(T, C, dtype=F64)
+    q_start, slots = step.q_start.tolist(), step.state_slots.tolist()
+    for s in range(step.num_seqs):
+        a, e = q_start[s], q_start[s + 1]
+        if e == a:
+            continue
+        full = torch.cat([state[slots[s]].to(F64), x64[a:e]], dim=0)
+        acc = torch.zeros(e - a, C, dtype=F64)
+        for j in range(L):
+            acc += taps[:, j].to(F64)[None, :] * full[j : j + e - a]
+        if bias is not None:
+            acc += bias.to(F64)[None, :]
+        y[a:e] = acc
+        state[slots[s]] = full[-(L - 1):].to(state.dtype)
+    if silu:
+        y = y * _sigmoid(y)
+    return y.to(x.dtype)
+
+
+def state_recurrence(q, k, v, state, step, heads, groups, dim, vdim, *, silu_inputs=False, head_loss=None,
+                     dt=None, dt_bias=None, a_log=None, skip=None):
+    """Per head ``S[dim, vdim]``: ``S = a S + b k v^T``, ``o = S^T q + skip v``.  With ``head_loss``:
+    ``a = 1 - head_loss[h]``, ``b = 1``.  With ``dt``: ``b = softplus(dt + dt_bias[h])``,
+    ``a = exp(-exp(a_log[h]) b)``.  Head ``h`` reads q and k of group ``h // (heads / groups)``;
+    ``silu_inputs`` applies silu to q, k and v first.  Returns float32 ``[T, heads * vdim]``."""
+    T = q.shape[0]
+    q64, k64, v64 = q.to(F64), k.to(F64), v.to(F64)
+    if silu_inputs:
+        q64, k64, v64 = q64 * _sigmoid(q64), k64 * _sigmoid(k64), v64 * _sigmoid(v64)
+    per = heads // groups
+    q64 = q64.reshape(T, groups, dim).repeat_interleave(per, dim=1)
+    k64 = k64.reshape(T, groups, dim).repeat_interleave(per, dim=1)
+    v64 = v64.reshape(T, heads, vdim)
+    if dt is not None:
+        z = dt.to(F64) + dt_bias.to(F64)
+        b = torch.where(z > 30.0, z, torch.log1p(torch.exp(torch.clamp(z, max=30.0))))
+        a = torch.exp(-torch.exp(a_log.to(F64)) * b)
+    else:
+        a = (1.0 - head_loss.to(F64))[None, :].expand(T, heads)
+        b = torch.ones(T, heads, dtype=F64)
+    o = torch.zeros(T, heads, vdim, dtype=F64)
+    q_start, slots = step.q_start.tolist(), step.state_slots.tolist()
+    for s in range(step.num_seqs):
+        if q_start[s + 1] == q_start[s]:
+            continue
+        S = state[slots[s]].to(F64)
+        for t in range(q_start[s], q_start[s + 1]):
+            S = a[t][:, None, None] * S + b[t][:, None, None] * k64[t][:, :, None] * v64[t][:, None, :]
+            o[t] = torch.einsum("hi,hij->hj", q64[t], S)
+        state[slots[s]] = S.to(state.dtype)
+    if skip is not None:
+        o = o + skip.to(F64)[None, :, None] * v64
+    return o.reshape(T, heads * vdim).to(torch.float32)
+
+
+def group_rmsnorm(x, weight, eps, groups, out_dtype, gate=None, gate_mode=None):
+    """Rows in ``groups`` equal parts, each divided by its own root mean square, times ``weight``.
+    ``gate_mode`` ``"silu_before"``: the rows are multiplied by ``silu(gate)`` first;
+    ``"sigmoid_after"``: the result is multiplied by ``sigmoid(gate)``."""
+    T, W = x.shape
+    y = x.to(F64)
+    if gate_mode == "silu_before":
+        g = gate.to(F64)
+        y = y * g * _sigmoid(g)
+    y = y.reshape(T, groups, W // groups)
+    y = (y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps)).reshape(T, W) * weight.to(F64)
+    if gate_mode == "sigmoid_after":
+        y = y * _sigmoid(gate.to(F64))
+    return y.to(out_dtype)
+
+
+# --------------------------------------------------------------------------- latent attention
+
+
+def _rotate_rows(v, positions, inv_freq, rotary_dim):
+    if not rotary_dim:
+        return v
+    half = rotary_dim // 2
+    angle = positions.to(F64)[:, None] * inv_freq.to(F64)[None, :]
+    cos, sin = torch.cos(angle), torch.sin(angle)
+    while cos.dim() < v.dim():
+        cos, sin = cos.unsqueeze(1), sin.unsqueeze(1)
+    out = v.clone()
+    a, b = v[..., :half], v[..., half:rotary_dim]
+    out[..., :half] = a * cos - b * sin
+    out[..., half:rotary_dim] = b * cos + a * sin
+    return out
+
+
+def latent_store(rows, rank, norm_w, eps, inv_freq, rotary_dim, step, k_cache, block_table, page_size):
+    """Each row ``[latent (rank) | shared key part]``: the latent RMS-normed with ``norm_w``, the
+    rest rotated by the row's position; stored as the position's row of the cache."""
+    x = rows.to(F64)
+    c = x[:, :rank]
+    c = c / torch.sqrt((c * c).mean(-1, keepdim=True) + eps) * norm_w.to(F64)
+    shared = _rotate_rows(x[:, rank:], step.positions, inv_freq, rotary_dim)
+    at = _cache_rows(block_table, step.seq_of_token, step.positions, page_size)
+    k_cache.view(-1, k_cache.shape[-1])[at] = torch.cat([c, shared], dim=-1).to(k_cache.dtype)
+
+
+def rotate_heads(x, out, inv_freq, rotary_dim, step):
+    """``x[T, H, P]`` rotated by each row's position into ``out[T, H, P]`` (both may be column ranges)."""
+    out.copy_(_rotate_rows(x.to(F64), step.positions, inv_freq, rotary_dim).to(out.dtype))
+
+
+def head_linear(x, w, out, gate=None):
+    """``out[t, h] = w[h] x[t, h]`` for ``x[T, H, K]``, ``w[H, N, K]``, ``out[T, H, N]``; with
+    ``gate[T, H]`` the head's result is multiplied by ``sigmoid(gate[t, h])``."""
+    y = torch.einsum("thk,hnk->thn", x.to(F64), w.to(F64))
+    if gate is not None:
+        y = y * _sigmoid(gate.to(F64))[:, :, None]
+    out.copy_(y.to(out.dtype))
+
+
+def latent_attention(q_lat, rank, k_cache, block_table, page_size, scale, step):
+    """Causal softmax attention of ``q_lat[T, H, D]`` against cached rows of ``D``; the values are
+    the first ``rank`` entries of the same rows.  Returns ``[T, H, rank]``."""
+    T, H, D = q_lat.shape
+    q64 = q_lat.to(F64)
+    kf = k_cache.view(-1, D)
+    out = torch.zeros(T, H, rank, dtype=F64)
+    seq, pos = step.seq_of_token.tolist(), step.positions.tolist()
+    for t in range(T):
+        ps = torch.arange(0, pos[t] + 1)
+        at = block_table[seq[t]].long()[ps // page_size] * page_size + ps % page_size
+        k = kf[at].to(F64)
+        p = torch.softmax((q64[t] @ k.T) * scale, dim=-1)  # [H, n]
+        out[t] = p @ k[:, :rank]
+    return out.to(q_lat.dtype)
+
+
+# --------------------------------------------------------------------------- mixture of experts
+
+
+def moe_route(logits, top, group_count, group_keep, scale, sigmoid=False, renormalize=False):
+    """Expert ids (int32 ``[T, top]``, best first) and weights (float32) of every row."""
+    T, E = logits.shape
+    z = logits.to(F64)
+    s = _sigmoid(z) if sigmoid else torch.softmax(z, dim=-1)
+    per = E // group_count
+    best = s.reshape(T, group_count, per).max(-1).values
+    order = torch.sort(best, dim=-1, descending=True, stable=True).indices[:, :group_keep]
+    kept = torch.zeros(T, group_count, dtype=torch.bool, device=logits.device)
+    kept.scatter_(1, order, True)
+    allowed = kept[:, :, None].expand(T, group_count, per).reshape(T, E)
+    masked = torch.where(allowed, s, torch.full_like(s, -1.0))
+    ids = torch.sort(masked, dim=-1, descending=True, stable=True).indices[:, :top]
+    w = torch.gather(s, 1, ids)
+    if renormalize:
+        w = w / w.sum(-1, keepdim=True)
+    return ids.to(torch.int32), (w * scale).to(torch.float32)
+
+
+def routed_experts(x, ids, weights, gate_up, down, extra=None):
+    """``sum_j weights[t, j] * expert_{ids[t, j]}(x[t])`` (+ ``extra``), in ``x``'s type."""
+    T, H = x.shape
+    x64 = x.to(F64)
+    out = torch.zeros(T, H, dtype=F64) if extra is None else extra.to(F64).clone()
+    inter = gate_up.shape[1] // 2
+    for t in range(T):
+        for j in range(ids.shape[1]):
+            e = int(ids[t, j])
+            y = gate_up[e].to(F64) @ x64[t]
+            g, u = y[:inter], y[inter:]
+            mid = (g * _sigmoid(g) * u)
+            out[t] += float(weights[t, j]) * (down[e].to(F64) @ mid)
+    return out.to(x.dtype)
