@@ -1,0 +1,333 @@
+// Products in batches of small matrices, and the routing of a mixture of experts.
+//
+// tile_gemm_kernel: out[m, b, :] = W[b] x[m, b, :] for batches b that are either the heads of one
+// row (x, out: [M, batches, .] with row and batch strides) or experts that own a range of rows
+// (rows grouped by expert, the ranges given by per-expert counts; the input row of grouped row m is
+// gather[m] / gather_div).  CUDA cores, float accumulation, a tile of 32 rows x 64 outputs per CTA
+// and 32 columns of K per pass; an output's sum runs over K in order, whatever else is in its tile, so
+// a row's result does not depend on the batch.  Epilogues: none; times sigmoid(gate[m, b]); or, for
+// a matrix that stacks gate over up rows, silu(gate) * up.
+//
+// Routing: moe_route_kernel (a warp per row: scores, group-limited choice of the top experts,
+// weights), moe_count / moe_place (rows grouped by expert with two passes of integer atomics:
+// which place a row gets inside its expert's range is arbitrary, its arithmetic is not touched by
+// it), moe_combine_kernel (a token's weighted sum over its choices, in the order of the choices).
+#include "common.cuh"
+
+#define TG_BM 32
+#define TG_BN 64
+#define TG_BK 32
+#define MOE_MAX_EXPERTS 256
+#define MOE_MAX_TOP 16
+
+struct TileGemmArgs {
+    const void* x;
+    long long x_ld, x_bs;
+    const int* gather;
+    int gather_div;
+    const void* w;
+    long long w_bs;
+    void* out;
+    long long out_ld, out_bs;
+    const int* counts;  // per-batch row counts (rows grouped by batch), or nullptr: every batch has rows 0..M-1
+    const void* gate;
+    long long gate_ld;
+    int M, N, K, batches;
+};
+
+template <typename XT, typename WT, typename OT, bool GLU>
+__global__ void __launch_bounds__(256) tile_gemm_kernel(const TileGemmArgs a) {
+    __shared__ float xs[TG_BK][TG_BM + 1];
+    __shared__ float ws[GLU ? 2 : 1][TG_BK][TG_BN + 1];
+    __shared__ int s_batch, s_row0, s_rows;
+    const int tid = threadIdx.x;
+    pdl_wait();
+    int batch, row0, row_end;
+    if (a.counts) {
+        // blockIdx.y counts row tiles over all batches: find the batch this tile falls into
+        if (tid == 0) {
+            int tile = blockIdx.y, start = 0, b = 0, found = -1;
+            for (; b < a.batches; ++b) {
+                const int c = a.counts[b], tiles = (c + TG_BM - 1) / TG_BM;
+                if (tile < tiles) { found = b; break; }
+                tile -= tiles;
+                start += c;
+            }
+            s_batch = found;
+            s_row0 = start + tile * TG_BM;
+            s_rows = found >= 0 ? start + a.counts[found] : 0;
+        }
+        __syncthreads();
+        batch = s_batch, row0 = s_row0, row_end = s_rows;
+        if (batch < 0) return;
+    } else {
+        batch = blockIdx.z, row0 = blockIdx.y * TG_BM, row_end = a.M;
+        if (row0 >= row_end) return;
+    }
+    const int n0 = blockIdx.x * TG_BN;
+    const XT* x = (const XT*)a.x + (size_t)batch * a.x_bs;
+    const WT* w = (const WT*)a.w + (size_t)batch * a.w_bs;
+    const int ty = tid >> 4, tx = tid & 15;  // rows ty*2, ty*2+1; outputs tx + 16 j
+    float acc[2][4] = {}, acc2[2][4] = {};
+    // which input row each of this thread's loads comes from (fixed over the K loop)
+    const int lrow = tid >> 3, lk = (tid & 7) * 4;  // x tile: 32 rows x 32 k: 8 threads a row, 4 k each
+    long long xrow = -1;
+    if (row0 + lrow < row_end) {
+        const int m = row0 + lrow;
+        xrow = a.gather ? a.gather[m] / a.gather_div : m;
+    }
+    for (int k0 = 0; k0 < a.K; k0 += TG_BK) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int k = k0 + lk + e;
+            xs[lk + e][lrow] = (xrow >= 0 && k < a.K) ? to_f32(x[(size_t)xrow * a.x_ld + k]) : 0.0f;
+        }
+        // w tile: 64 outputs x 32 k: 4 threads an output row, 8 k each
+        {
+            const int wn = tid >> 2, wk = (tid & 3) * 8;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const int k = k0 + wk + e, n = n0 + wn;
+                const bool ok = n < a.N && k < a.K;
+                ws[0][wk + e][wn] = ok ? to_f32(w[(size_t)n * a.K + k]) : 0.0f;
+                if (GLU) ws[1][wk + e][wn] = ok ? to_f32(w[(size_t)(a.N + n) * a.K + k]) : 0.0f;
+            }
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < TG_BK; ++k) {
+            const float x0 = xs[k][ty * 2], x1 = xs[k][ty * 2 + 1];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float wv = ws[0][k][tx + 16 * j];
+                acc[0][j] = fmaf(x0, wv, acc[0][j]);
+                acc[1][j] = fmaf(x1, wv, acc[1][j]);
+                if (GLU) {
+                    const float uv = ws[1][k][tx + 16 * j];
+                    acc2[0][j] = fmaf(x0, uv, acc2[0][j]);
+                    acc2[1][j] = fmaf(x1, uv, acc2[1][j]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    pdl_trigger();
+    OT* out = (OT*)a.out + (size_t)batch * a.out_bs;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int m = row0 + ty * 2 + i;
+        if (m >= row_end) continue;
+        float scale = 1.0f;
+        if (a.gate) scale = 1.0f / (1.0f + expf(-to_f32(((const XT*)a.gate)[(size_t)m * a.gate_ld + batch])));
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int n = n0 + tx + 16 * j;
+            if (n >= a.N) continue;
+            float v = acc[i][j];
+            if (GLU) v = v / (1.0f + expf(-v)) * acc2[i][j];
+            out[(size_t)m * a.out_ld + n] = from_f32<OT>(v * scale);
+        }
+    }
+}
+
+template <bool GLU>
+static int launch_tile_gemm(const TileGemmArgs& a, int x_dtype, int w_dtype, int out_dtype, int row_tiles, int z, cudaStream_t stream) {
+    const dim3 grid((a.N + TG_BN - 1) / TG_BN, row_tiles, z);
+    typedef __nv_bfloat16 bf;
+#define TG_GO(XT, WT, OT)                                                                 \
+    {                                                                                     \
+        launch_kernel(tile_gemm_kernel<XT, WT, OT, GLU>, grid, dim3(256), 0, stream, a);  \
+        return launch_status();                                                           \
+    }
+    if (x_dtype == SHISO_F32 && w_dtype == SHISO_F32 && out_dtype == SHISO_F32) TG_GO(float, float, float)
+    if (x_dtype == SHISO_BF16 && w_dtype == SHISO_BF16 && out_dtype == SHISO_BF16) TG_GO(bf, bf, bf)
+    if (x_dtype == SHISO_BF16 && w_dtype == SHISO_BF16 && out_dtype == SHISO_F32) TG_GO(bf, bf, float)
+    if (x_dtype == SHISO_BF16 && w_dtype == SHISO_F32 && out_dtype == SHISO_BF16) TG_GO(bf, float, bf)
+    if (x_dtype == SHISO_BF16 && w_dtype == SHISO_F32 && out_dtype == SHISO_F32) TG_GO(bf, float, float)
+#undef TG_GO
+    return SHISO_ERR_DTYPE;
+}
+
+// out[t, h, :] = W[h] x[t, h, :] (times sigmoid(gate[t, h])): x [T, H, K] and out [T, H, N] with row and head strides.
+SHISO_API int shiso_head_linear(const void* x, long long x_ld, long long x_hs, int x_dtype, const void* w, int w_dtype, void* out,
+                                long long out_ld, long long out_hs, int out_dtype, const void* gate, long long gate_ld, int tokens,
+                                int heads, int n, int k, cudaStream_t stream) {
+    if (tokens <= 0 || heads <= 0 || n <= 0) return SHISO_OK;
+    if (k <= 0 || heads > 65535) return SHISO_ERR_SHAPE;
+    TileGemmArgs a = {x, x_ld, x_hs, nullptr, 1, w, (long long)n * k, out, out_ld, out_hs, nullptr, gate, gate_ld, tokens, n, k, heads};
+    return launch_tile_gemm<false>(a, x_dtype, w_dtype, out_dtype, (tokens + TG_BM - 1) / TG_BM, heads, stream);
+}
+
+// --------------------------------------------------------------------------- routing
+
+// A warp per row.  scores = softmax(logits) (or sigmoids); experts in `group_count` groups of
+// neighbours, a group's score its largest; the `group_keep` best groups stay; among their experts
+// the `top` largest scores win (the lower index on a tie); weight = score (/ the chosen scores'
+// sum) * scale.
+__global__ void moe_route_kernel(const float* __restrict__ logits, int* __restrict__ ids, float* __restrict__ weights, int tokens,
+                                 int experts, int top, int group_count, int group_keep, float scale, int sigmoid, int renormalize) {
+    pdl_begin();
+    __shared__ float s_scores[8][MOE_MAX_EXPERTS];
+    __shared__ float s_group[8][MOE_MAX_EXPERTS];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * 8 + warp;
+    if (t >= tokens) return;
+    float* sc = s_scores[warp];
+    float* gs = s_group[warp];
+    const float* z = logits + (size_t)t * experts;
+    float mx = -INFINITY;
+    for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, z[e]);
+    mx = warp_max(mx);
+    float sum = 0.0f;
+    for (int e = lane; e < experts; e += 32) {
+        const float v = sigmoid ? 1.0f / (1.0f + expf(-z[e])) : expf(z[e] - mx);
+        sc[e] = v;
+        sum += v;
+    }
+    sum = warp_sum(sum);
+    if (!sigmoid) {
+        const float inv = 1.0f / sum;
+        for (int e = lane; e < experts; e += 32) sc[e] *= inv;
+    }
+    __syncwarp();
+    const int per = experts / group_count;
+    for (int g = lane; g < group_count; g += 32) {
+        float best = -1.0f;
+        for (int e = 0; e < per; ++e) best = fmaxf(best, sc[g * per + e]);
+        gs[g] = best;
+    }
+    __syncwarp();
+    // the groups that stay: group_keep times the best remaining one; a kept group's score becomes 2 (above any score), a dropped one's stays
+    for (int r = 0; r < group_keep; ++r) {
+        float best = -2.0f;
+        int at = 0x7fffffff;
+        for (int g = lane; g < group_count; g += 32) {
+            const float v = gs[g];
+            if (v <= 1.5f && (v > best || (v == best && g < at))) best = v, at = g;
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ov > best || (ov == best && oa < at)) best = ov, at = oa;
+        }
+        if (lane == 0) gs[at] = 2.0f;
+        __syncwarp();
+    }
+    float chosen_sum = 0.0f;
+    float my_w = 0.0f;
+    int my_id = 0;
+    for (int r = 0; r < top; ++r) {
+        float best = -2.0f;
+        int at = 0x7fffffff;
+        for (int e = lane; e < experts; e += 32) {
+            const float v = sc[e];
+            if (v >= 0.0f && gs[e / per] > 1.5f && (v > best || (v == best && e < at))) best = v, at = e;
+        }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ov > best || (ov == best && oa < at)) best = ov, at = oa;
+        }
+        chosen_sum += best;
+        if (lane == r) my_w = best, my_id = at;
+        if (lane == 0) sc[at] = -1.0f;  // taken
+        __syncwarp();
+    }
+    if (lane < top) {
+        ids[(size_t)t * top + lane] = my_id;
+        weights[(size_t)t * top + lane] = (renormalize ? my_w / chosen_sum : my_w) * scale;
+    }
+}
+
+SHISO_API int shiso_moe_route(const float* logits, int* ids, float* weights, int tokens, int experts, int top, int group_count,
+                              int group_keep, float scale, int sigmoid, int renormalize, cudaStream_t stream) {
+    if (tokens <= 0) return SHISO_OK;
+    if (experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0 || top > MOE_MAX_TOP || top > experts || group_count <= 0 ||
+        experts % group_count || group_keep <= 0 || group_keep > group_count || group_keep * (experts / group_count) < top)
+        return SHISO_ERR_SHAPE;
+    launch_kernel(moe_route_kernel, ceil_div_u(tokens, 8), 256, 0, stream, logits, ids, weights, tokens, experts, top, group_count,
+                  group_keep, scale, sigmoid, renormalize);
+    return launch_status();
+}
+
+__global__ void moe_zero_kernel(int* __restrict__ counts, int experts) {
+    pdl_begin();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
+}
+
+__global__ void moe_count_kernel(const int* __restrict__ ids, int* __restrict__ counts, int* __restrict__ rank, int total) {
+    pdl_begin();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) rank[i] = atomicAdd(&counts[ids[i]], 1);
+}
+
+// place[i] = first row of the choice's expert + its rank there; source[place] = i
+__global__ void moe_place_kernel(const int* __restrict__ ids, const int* __restrict__ counts, const int* __restrict__ rank,
+                                 int* __restrict__ place, int* __restrict__ source, int total, int experts) {
+    pdl_begin();
+    __shared__ int first[MOE_MAX_EXPERTS];
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < experts; ++e) {
+            first[e] = at;
+            at += counts[e];
+        }
+    }
+    __syncthreads();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const int p = first[ids[i]] + rank[i];
+    place[i] = p;
+    source[p] = i;
+}
+
+// out[t] = extra[t] + sum_j weights[t, j] * y[place[t * top + j]], the choices in their order
+template <typename AT>
+__global__ void moe_combine_kernel(const float* __restrict__ y, const int* __restrict__ place, const float* __restrict__ weights,
+                                   const AT* __restrict__ extra, AT* __restrict__ out, int tokens, int hidden, int top) {
+    pdl_begin();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)tokens * hidden) return;
+    const int t = (int)(i / hidden), c = (int)(i % hidden);
+    float acc = 0.0f;
+    for (int j = 0; j < top; ++j) acc = fmaf(weights[(size_t)t * top + j], y[(size_t)place[(size_t)t * top + j] * hidden + c], acc);
+    if (extra) acc += to_f32(extra[i]);
+    out[i] = from_f32<AT>(acc);
+}
+
+// The experts of one step.  ids / weights [T, top]; gate_up [E, 2 ff, hidden]; down [E, hidden, ff];
+// scratch: ints [E + 3 * T * top], mid [T * top, ff] (activation type), y [T * top, hidden] (float).
+SHISO_API int shiso_routed_experts(const void* x, int act_dtype, const int* ids, const float* weights, const void* gate_up,
+                                   const void* down, int w_dtype, const void* extra, void* out, int* ints, void* mid, float* y,
+                                   int tokens, int hidden, int ff, int experts, int top, cudaStream_t stream) {
+    if (tokens <= 0) return SHISO_OK;
+    if (experts <= 0 || experts > MOE_MAX_EXPERTS || top <= 0 || hidden <= 0 || ff <= 0) return SHISO_ERR_SHAPE;
+    const int total = tokens * top;
+    int* counts = ints;
+    int* rank = ints + experts;
+    int* place = rank + total;
+    int* source = place + total;
+    launch_kernel(moe_zero_kernel, 1, 256, 0, stream, counts, experts);
+    launch_kernel(moe_count_kernel, ceil_div_u(total, 256), 256, 0, stream, ids, counts, rank, total);
+    launch_kernel(moe_place_kernel, ceil_div_u(total, 256), 256, 0, stream, ids, (const int*)counts, (const int*)rank, place, source,
+                  total, experts);
+    int status = launch_status();
+    if (status) return status;
+    const int row_tiles = (total + TG_BM - 1) / TG_BM + experts;  // every expert may end in a tile that is not full
+    TileGemmArgs up = {x, hidden, 0, source, top, gate_up, (long long)2 * ff * hidden, mid, ff, 0, counts, nullptr, 0, total, ff, hidden, experts};
+    status = launch_tile_gemm<true>(up, act_dtype, w_dtype, act_dtype, row_tiles, 1, stream);
+    if (status) return status;
+    TileGemmArgs dn = {mid, ff, 0, nullptr, 1, down, (long long)hidden * ff, y, hidden, 0, counts, nullptr, 0, total, hidden, ff, experts};
+    status = launch_tile_gemm<false>(dn, act_dtype, w_dtype, SHISO_F32, row_tiles, 1, stream);
+    if (status) return status;
+    const unsigned blocks = ceil_div_u((long long)tokens * hidden, 256);
+    if (act_dtype == SHISO_F32)
+        launch_kernel(moe_combine_kernel<float>, blocks, 256, 0, stream, (const float*)y, (const int*)place, weights, (const float*)extra,
+                      (float*)out, tokens, hidden, top);
+    else if (act_dtype == SHISO_BF16)
+        launch_kernel(moe_combine_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const float*)y, (const int*)place, weights,
+                      (const __nv_bfloat16*)extra, (__nv_bfloat16*)out, tokens, hidden, top);
+    else
+        return SHISO_ERR_DTYPE;
+    return launch_status();
+}

@@ -1,0 +1,167 @@
+// Matrix-state recurrences with one scalar decay per head and token:
+//
+//     S_t = a_t S_{t-1} + b_t k_t v_t^T,        o_t = S_t^T q_t + skip_h v_t,
+//
+// S[dim, vdim] per head, float, carried per request in its state slot.  Two ways to give a and b:
+// a fixed decay per head (loss_h = 1 - decay_h; S - loss S is formed, so that a decay near one
+// loses nothing to its own rounding; b = 1), or a step size per token and head, dt, with
+// b = softplus(dt + dt_bias_h) and a = exp(-exp(a_log_h) b).  q and k may be shared by the heads of
+// a group (head h reads group h / (heads / groups)); silu may be applied to q, k and v on load.
+//
+// One CTA walks the rows of one (head, sequence, range of value columns) in order.  A warp holds 8
+// columns; the key rows of a column are dealt to 4 lanes (row n to lane n % 4), so a lane keeps
+// dim / 4 state values in registers and an output is a sum over a lane's rows followed by two
+// shuffles: what is added to what, and in which order, depends on dim only - never on how the
+// sequence was cut into steps, on the batch, or on how many columns a CTA was given.  Rows are
+// staged in shared memory sixteen at a time (activations and the two exponentials applied once, on
+// the way in).  Outputs are float rows [T, heads * vdim]: the norm and gate that follow them are a
+// row kernel's.
+#include "common.cuh"
+
+#define SR_TOKENS 16
+
+struct StateRecurrenceArgs {
+    const void *q, *k, *v, *dt;
+    long long q_ld, k_ld, v_ld, dt_ld;
+    const float *dt_bias, *a_log, *skip, *head_loss;
+    float* state;
+    long long slot_stride;
+    const int *q_start, *state_slots;
+    float* out;
+    int heads, groups, dim, vdim, cols, silu;
+};
+
+__device__ __forceinline__ float sr_silu(float z) { return z / (1.0f + expf(-z)); }
+
+template <typename AT, int RPT>
+__global__ void __launch_bounds__(256) state_recurrence_kernel(const StateRecurrenceArgs a) {
+    const int h = blockIdx.x, s = blockIdx.y, col0 = blockIdx.z * a.cols;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int part = lane & 3, local = warp * 8 + (lane >> 2), col = col0 + local;
+    const bool live = col < a.vdim;
+    const int dim = a.dim, vdim = a.vdim, g = h / (a.heads / a.groups);
+    extern __shared__ float sm[];
+    float* sq = sm;                         // [SR_TOKENS][dim]
+    float* sk = sq + SR_TOKENS * dim;       // [SR_TOKENS][dim]
+    float* sv = sk + SR_TOKENS * dim;       // [SR_TOKENS][cols]
+    float* sa = sv + SR_TOKENS * a.cols;    // [SR_TOKENS]
+    float* sb = sa + SR_TOKENS;             // [SR_TOKENS]
+    const float skip = a.skip ? a.skip[h] : 0.0f;
+    const float loss = a.head_loss ? a.head_loss[h] : 0.0f;
+    const float rate = a.a_log ? expf(a.a_log[h]) : 0.0f;
+    const float dt_bias = a.dt_bias ? a.dt_bias[h] : 0.0f;
+    pdl_wait();
+    const int first = a.q_start[s], n = a.q_start[s + 1] - first;
+    if (n <= 0) return;
+    float* slot = a.state + (size_t)a.state_slots[s] * a.slot_stride + (size_t)h * dim * vdim;
+    float S[RPT];
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) {
+        const int row = part + 4 * r;
+        S[r] = (live && row < dim) ? slot[(size_t)row * vdim + col] : 0.0f;
+    }
+    const AT* qp = (const AT*)a.q + (size_t)g * dim;
+    const AT* kp = (const AT*)a.k + (size_t)g * dim;
+    const AT* vp = (const AT*)a.v + (size_t)h * vdim + col0;
+    const AT* dtp = a.dt ? (const AT*)a.dt + h : nullptr;
+    float* op = a.out + (size_t)h * vdim + col;
+    for (int base = 0; base < n; base += SR_TOKENS) {
+        const int count = min(SR_TOKENS, n - base);
+        const size_t row0 = (size_t)(first + base);
+        for (int i = threadIdx.x; i < count * dim; i += blockDim.x) {
+            const int t = i / dim, c = i - t * dim;
+            float qv = to_f32(qp[(row0 + t) * a.q_ld + c]), kv = to_f32(kp[(row0 + t) * a.k_ld + c]);
+            if (a.silu) qv = sr_silu(qv), kv = sr_silu(kv);
+            sq[t * dim + c] = qv;
+            sk[t * dim + c] = kv;
+        }
+        for (int i = threadIdx.x; i < count * a.cols; i += blockDim.x) {
+            const int t = i / a.cols, c = i - t * a.cols;
+            float vv = (col0 + c < vdim) ? to_f32(vp[(row0 + t) * a.v_ld + c]) : 0.0f;
+            if (a.silu) vv = sr_silu(vv);
+            sv[t * a.cols + c] = vv;
+        }
+        if (dtp) {
+            for (int t = threadIdx.x; t < count; t += blockDim.x) {
+                const float z = to_f32(dtp[(row0 + t) * a.dt_ld]) + dt_bias;
+                const float step = z > 20.0f ? z : log1pf(expf(z));
+                sb[t] = step;
+                sa[t] = expf(-rate * step);
+            }
+        }
+        __syncthreads();
+        for (int t = 0; t < count; ++t) {
+            const float* qt = sq + t * dim + part;
+            const float* kt = sk + t * dim + part;
+            const float vt = sv[t * a.cols + local];
+            float acc = 0.0f;
+            if (dtp) {
+                const float decay = sa[t], bv = sb[t] * vt;
+#pragma unroll
+                for (int r = 0; r < RPT; ++r) {
+                    if (part + 4 * r < dim) {
+                        S[r] = fmaf(decay, S[r], kt[4 * r] * bv);
+                        acc = fmaf(S[r], qt[4 * r], acc);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < RPT; ++r) {
+                    if (part + 4 * r < dim) {
+                        S[r] = fmaf(kt[4 * r], vt, fmaf(-loss, S[r], S[r]));
+                        acc = fmaf(S[r], qt[4 * r], acc);
+                    }
+                }
+            }
+            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+            if (live && part == 0) op[(row0 + t) * ((size_t)a.heads * vdim)] = fmaf(skip, vt, acc);
+        }
+        __syncthreads();
+    }
+    pdl_trigger();
+#pragma unroll
+    for (int r = 0; r < RPT; ++r) {
+        const int row = part + 4 * r;
+        if (live && row < dim) slot[(size_t)row * vdim + col] = S[r];
+    }
+}
+
+template <typename AT>
+static int launch_state_recurrence(const StateRecurrenceArgs& a, int num_seqs, int sm_count, cudaStream_t stream) {
+    // value columns per CTA: as few as keeps every SM busy, in steps a warp's 8 columns allow
+    int cols = 64;
+    while (cols > 8 && (long long)a.heads * num_seqs * ((a.vdim + cols - 1) / cols) < sm_count) cols /= 2;
+    while (cols > 8 && cols / 2 >= a.vdim) cols /= 2;
+    StateRecurrenceArgs args = a;
+    args.cols = cols;
+    const dim3 grid(a.heads, num_seqs, (a.vdim + cols - 1) / cols), block(cols * 4);
+    const size_t smem = (size_t)(2 * SR_TOKENS * a.dim + SR_TOKENS * cols + 2 * SR_TOKENS) * sizeof(float);
+    const int rpt = (a.dim + 3) / 4;
+#define SR_CASE(R)                                                                                                   \
+    if (rpt <= R) {                                                                                                  \
+        auto kern = state_recurrence_kernel<AT, R>;                                                                  \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
+        launch_kernel(kern, grid, block, smem, stream, args);                                                        \
+        return launch_status();                                                                                      \
+    }
+    SR_CASE(2) SR_CASE(4) SR_CASE(8) SR_CASE(16) SR_CASE(32) SR_CASE(64)
+#undef SR_CASE
+    return SHISO_ERR_SHAPE;
+}
+
+SHISO_API int shiso_state_recurrence(const void* q, const void* k, const void* v, const void* dt, long long q_ld, long long k_ld,
+                                     long long v_ld, long long dt_ld, int act_dtype, const float* dt_bias, const float* a_log,
+                                     const float* skip, const float* head_loss, float* state, long long slot_stride,
+                                     const int* q_start, const int* state_slots, float* out, int tokens, int num_seqs, int heads,
+                                     int groups, int dim, int vdim, int silu, int sm_count, cudaStream_t stream) {
+    if (tokens <= 0 || num_seqs <= 0) return SHISO_OK;
+    if (heads <= 0 || groups <= 0 || heads % groups || dim <= 0 || dim > 256 || vdim <= 0) return SHISO_ERR_SHAPE;
+    if ((dt != nullptr) == (head_loss != nullptr)) return SHISO_ERR_UNSUPPORTED;  // one of the two forms
+    if (dt && (!dt_bias || !a_log)) return SHISO_ERR_UNSUPPORTED;
+    StateRecurrenceArgs a = {q, k, v, dt, q_ld, k_ld, v_ld, dt_ld, dt_bias, a_log, skip, head_loss, state, slot_stride,
+                             q_start, state_slots, out, heads, groups, dim, vdim, 0, silu};
+    if (act_dtype == SHISO_F32) return launch_state_recurrence<float>(a, num_seqs, sm_count, stream);
+    if (act_dtype == SHISO_BF16) return launch_state_recurrence<__nv_bfloat16>(a, num_seqs, sm_count, stream);
+    return SHISO_ERR_DTYPE;
+}

@@ -259,20 +259,24 @@ SHISO_API int shiso_token_shift_blend(const void* h, int act_dtype, const float*
 
 // --------------------------------------------------------------------------- unary maps
 
-enum { SHISO_UNARY_TANH = 0, SHISO_UNARY_SILU = 1 };
+enum { SHISO_UNARY_TANH = 0, SHISO_UNARY_SILU = 1, SHISO_UNARY_RELU2 = 2 };  // relu2: the square of max(x, 0)
 
 template <typename IT, typename OT>
 __global__ void unary_kernel(const IT* __restrict__ x, OT* __restrict__ out, long long count, int kind) {
     pdl_begin();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (long long)gridDim.x * blockDim.x) {
         const float v = to_f32(x[i]);
-        out[i] = from_f32<OT>(kind == SHISO_UNARY_TANH ? tanhf(v) : v / (1.0f + expf(-v)));
+        float r;
+        if (kind == SHISO_UNARY_TANH) r = tanhf(v);
+        else if (kind == SHISO_UNARY_SILU) r = v / (1.0f + expf(-v));
+        else r = v > 0.0f ? v * v : 0.0f;
+        out[i] = from_f32<OT>(r);
     }
 }
 
 SHISO_API int shiso_unary(const void* x, int in_dtype, void* out, int out_dtype, long long count, int kind, cudaStream_t stream) {
     if (count <= 0) return SHISO_OK;
-    if (kind != SHISO_UNARY_TANH && kind != SHISO_UNARY_SILU) return SHISO_ERR_UNSUPPORTED;
+    if (kind < SHISO_UNARY_TANH || kind > SHISO_UNARY_RELU2) return SHISO_ERR_UNSUPPORTED;
     const unsigned blocks = (unsigned)((count + 255) / 256 < 4096 ? (count + 255) / 256 : 4096);
     if (in_dtype == SHISO_F32 && out_dtype == SHISO_F32)
         launch_kernel(unary_kernel<float, float>, blocks, 256, 0, stream, (const float*)x, (float*)out, count, kind);

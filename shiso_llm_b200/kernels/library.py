@@ -68,6 +68,17 @@ _SIGNATURES = {
     "shiso_pool_kv": [P, P, I, P, P, P, P, I, P, P, I, I, I, I, I, I, P],
     "shiso_pooled_window_attention": [P, LL, I, P, P, P, P, P, P, I, P, P, P, LL, P, I, I, I, I, I, I, F, I, I, F, P],
     "shiso_prefill_attention_tc_open": [P, LL, P, P, P, I, P, P, P, LL, P, F, I, I, I, I, I, I, LL, F, I, P],
+    "shiso_add_layernorm": [P, P, P, P, P, P, I, I, I, F, P],
+    "shiso_group_rmsnorm": [P, I, LL, P, LL, P, P, I, I, I, I, I, F, P],
+    "shiso_causal_conv": [P, LL, I, P, P, P, LL, P, P, P, P, I, I, I, I, I, P],
+    "shiso_rotate_heads": [P, LL, LL, P, LL, LL, I, P, P, I, I, I, I, P],
+    "shiso_latent_store": [P, LL, I, P, P, P, P, P, I, P, I, I, I, I, I, F, P],
+    "shiso_state_recurrence": [P, P, P, P, LL, LL, LL, LL, I, P, P, P, P, P, LL, P, P, P, I, I, I, I, I, I, I, I, P],
+    "shiso_head_linear": [P, LL, LL, I, P, I, P, LL, LL, I, P, LL, I, I, I, I, P],
+    "shiso_moe_route": [P, P, P, I, I, I, I, I, F, I, I, P],
+    "shiso_routed_experts": [P, I, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, P],
+    "shiso_latent_attention_smem": [I, I],
+    "shiso_latent_attention": [P, I, P, P, I, P, P, P, P, I, I, I, I, I, F, I, P],
 }
 
 

@@ -934,7 +934,7 @@ def token_shift_blend(x, mu, state, step):
     return out
 
 
-_UNARY = {"tanh": 0, "silu": 1}
+_UNARY = {"tanh": 0, "silu": 1, "relu2": 2}
 
 
 def unary(x, kind, out_dtype):
@@ -1118,6 +1118,293 @@ def pooled_window_attention(q, heads, k_cache, v_cache, block_table, pooled_k, p
         _ptr(seen), tokens, heads, kv_heads, dim, vdim, page_size, float(scale), int(window), int(pool), float(out_scale), _stream(),
     )
     _done(status, "pooled_window_attention" + (" (pooled blocks)" if seen is not None else ""), shape=(tokens, heads, dim))
+    return out
+
+
+# --------------------------------------------------------------------------- layer norm, norms in groups
+
+
+def add_layernorm(residual, deltas, w, eps, out_dtype, rows=None):
+    """Layer norm with a weight and no bias of ``residual`` (float32 ``[T, H]``) plus up to two
+    block outputs ``deltas`` (tensors of the output type); the sum is formed in float32 and,
+    without ``rows``, stored back.  With ``rows`` only those rows are summed and normalised."""
+    _check(residual, "residual", torch.float32, 2)
+    _check(w, "norm weight", torch.float32, 1)
+    tokens, hidden = residual.shape
+    if w.shape[0] != hidden:
+        raise KernelError(f"norm weight has {w.shape[0]} entries for rows of {hidden}")
+    deltas = tuple(deltas)
+    if len(deltas) > 2:
+        raise KernelError(f"{len(deltas)} block outputs wait to be added; the kernel takes two")
+    for d in deltas:
+        _check(d, "delta", out_dtype, 2)
+        if d.shape != residual.shape:
+            raise KernelError(f"delta {tuple(d.shape)} does not match the residual {tuple(residual.shape)}")
+    out_rows = tokens
+    if rows is not None:
+        _check(rows, "rows", torch.int32, 1)
+        out_rows = rows.shape[0]
+    out = torch.empty((out_rows, hidden), dtype=out_dtype, device=residual.device)
+    status = library().shiso_add_layernorm(
+        _ptr(residual), _ptr(deltas[0]) if deltas else 0, _ptr(deltas[1]) if len(deltas) > 1 else 0, _ptr(rows), _ptr(w), _ptr(out),
+        _code(out), out_rows, hidden, float(eps), _stream(),
+    )
+    _done(status, "layernorm" if not deltas else f"add {len(deltas)} + layernorm", shape=(out_rows, hidden))
+    return out
+
+
+_GATE_MODES = {None: 0, "silu_before": 1, "sigmoid_after": 2}
+
+
+def group_rmsnorm(x, weight, eps, groups, out_dtype, gate=None, gate_mode=None):
+    """Rows ``x[T, W]`` (float32 or the output type; a column range may be given) in ``groups`` equal
+    parts, each divided by its own root mean square, times ``weight``.  ``gate_mode``
+    ``"silu_before"`` multiplies the rows by ``silu(gate)`` first, ``"sigmoid_after"`` the result by
+    ``sigmoid(gate)``; ``gate`` is ``[T, W]`` of the output type (a column range may be given)."""
+    tokens, width = x.shape
+    x_ld = _rows(x, "x", None, width)
+    if x.dtype not in (torch.float32, out_dtype):
+        raise KernelError(f"rows of {x.dtype} for an output of {out_dtype}")
+    _check(weight, "norm weight", torch.float32, 1)
+    if weight.shape[0] != width or groups < 1 or width % groups:
+        raise KernelError(f"a weight of {weight.shape[0]} or {groups} groups for rows of {width}")
+    if (gate is None) != (gate_mode is None) or gate_mode not in _GATE_MODES:
+        raise KernelError(f"gate mode {gate_mode!r} with{'out' if gate is None else ''} a gate")
+    gate_ld = _rows(gate, "gate", out_dtype, width) if gate is not None else 0
+    out = torch.empty((tokens, width), dtype=out_dtype, device=x.device)
+    status = library().shiso_group_rmsnorm(
+        x.data_ptr(), _code(x), x_ld, gate.data_ptr() if gate is not None else 0, gate_ld, _ptr(weight), _ptr(out), _code(out),
+        tokens, width, int(groups), _GATE_MODES[gate_mode], float(eps), _stream(),
+    )
+    _done(status, "group_rmsnorm", shape=(tokens, width, groups))
+    return out
+
+
+# --------------------------------------------------------------------------- causal convolution, scalar-decay recurrences
+
+
+def causal_conv(x, taps, bias, state, step, silu=True):
+    """``y_t[c] = act(bias[c] + sum_j taps[c, j] x_{t-(L-1)+j}[c])`` per sequence (``x[T, C]``, a column
+    range may be given); ``state`` (float32 ``[slots, L-1, C]``) holds each request's last ``L - 1``
+    inputs and is brought up to date."""
+    tokens, channels = x.shape
+    x_ld = _rows(x, "x", None, channels)
+    _check(taps, "conv taps", torch.float32, 2)
+    n_taps = taps.shape[1]
+    if taps.shape[0] != channels:
+        raise KernelError(f"taps for {taps.shape[0]} channels, rows of {channels}")
+    if bias is not None:
+        _check(bias, "conv bias", torch.float32, 1)
+    if state.shape[1:] != (n_taps - 1, channels):
+        raise KernelError(f"conv state of shape {tuple(state.shape)} does not fit {n_taps} taps x {channels}")
+    stride = _slot_rows(state, "conv state", torch.float32)
+    y = torch.empty((tokens, channels), dtype=x.dtype, device=x.device)
+    status = library().shiso_causal_conv(
+        x.data_ptr(), x_ld, _code(x), _ptr(taps), _ptr(bias), state.data_ptr(), stride, _ptr(step.seq_of_token), _ptr(step.q_start),
+        _ptr(step.state_slots), _ptr(y), tokens, step.num_seqs, channels, n_taps, int(bool(silu)), _stream(),
+    )
+    _done(status, "causal_conv", 2, shape=(tokens, channels))
+    return y
+
+
+def state_recurrence(q, k, v, state, step, heads, groups, dim, vdim, *, silu_inputs=False, head_loss=None,
+                     dt=None, dt_bias=None, a_log=None, skip=None):
+    """A matrix state ``S[dim, vdim]`` per head (``state``, float32 ``[slots, heads, dim, vdim]``) walked
+    over each sequence's rows in order: ``S = a S + b k v^T``, ``o = S^T q + skip v``.  With
+    ``head_loss`` (float32 ``[heads]``, one minus the head's decay): ``a = 1 - head_loss``, ``b = 1``.
+    With ``dt`` (``[T, heads]``): ``b = softplus(dt + dt_bias)``, ``a = exp(-exp(a_log) b)``.  q and k
+    are ``[T, groups * dim]``, head ``h`` reading group ``h // (heads / groups)``; ``silu_inputs``
+    applies silu to q, k and v on load.  All inputs may be column ranges.  Returns float32
+    ``[T, heads * vdim]``."""
+    act = q.dtype
+    tokens = q.shape[0]
+    q_ld, k_ld = _rows(q, "q", act, groups * dim), _rows(k, "k", act, groups * dim)
+    v_ld = _rows(v, "v", act, heads * vdim)
+    if state.shape[1:] != (heads, dim, vdim):
+        raise KernelError(f"a state of shape {tuple(state.shape)} for {heads} heads of {dim} x {vdim}")
+    stride = _slot_rows(state, "recurrent state", torch.float32)
+    if (dt is None) == (head_loss is None):
+        raise KernelError("a recurrence takes either a decay per head or a step size per token and head")
+    dt_ld = 0
+    if dt is not None:
+        dt_ld = _rows(dt, "dt", act, heads)
+        for name, t in (("dt bias", dt_bias), ("a_log", a_log)):
+            _check(t, name, torch.float32, 1)
+            if t.shape[0] != heads:
+                raise KernelError(f"{name} has {t.shape[0]} entries for {heads} heads")
+    else:
+        _check(head_loss, "head loss", torch.float32, 1)
+        if head_loss.shape[0] != heads:
+            raise KernelError(f"{head_loss.shape[0]} values of 1 - decay for {heads} heads")
+    if skip is not None:
+        _check(skip, "skip", torch.float32, 1)
+        if skip.shape[0] != heads:
+            raise KernelError(f"{skip.shape[0]} skip weights for {heads} heads")
+    out = torch.empty((tokens, heads * vdim), dtype=torch.float32, device=q.device)
+    status = library().shiso_state_recurrence(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), dt.data_ptr() if dt is not None else 0, q_ld, k_ld, v_ld, dt_ld, _CODES[act],
+        _ptr(dt_bias), _ptr(a_log), _ptr(skip), _ptr(head_loss), state.data_ptr(), stride, _ptr(step.q_start), _ptr(step.state_slots),
+        _ptr(out), tokens, step.num_seqs, heads, groups, dim, vdim, int(bool(silu_inputs)), _sm_count(), _stream(),
+    )
+    _done(status, "state_recurrence", shape=(tokens, heads, dim, vdim))
+    return out
+
+
+# --------------------------------------------------------------------------- latent attention
+
+
+def _heads3(t, name, dtype):
+    """Row and head strides of ``[T, H, W]`` whose last dimension is contiguous."""
+    if not t.is_cuda or t.dim() != 3 or (t.shape[2] > 1 and t.stride(2) != 1) or (dtype is not None and t.dtype != dtype):
+        raise KernelError(f"{name}: expected [T, H, W] CUDA rows of {dtype} with unit column stride, got {t.dtype} {tuple(t.shape)} {t.stride()}")
+    return t.stride(0), t.stride(1)
+
+
+def latent_store(rows, rank, norm_w, eps, inv_freq, rotary_dim, step, k_cache, block_table, page_size):
+    """Each row ``[latent (rank) | shared key part]`` (a column range may be given): the latent
+    RMS-normed with ``norm_w``, the rest rotated by the row's position (half-split pairs over
+    ``rotary_dim``); stored as the position's row of ``k_cache [pages, page_size, 1, width]``."""
+    tokens, width = rows.shape
+    ld = _rows(rows, "rows", k_cache.dtype, width)
+    _paged(k_cache, "latent cache", rows.dtype, page_size)
+    if k_cache.shape[2:] != (1, width):
+        raise KernelError(f"a cache of shape {tuple(k_cache.shape)} for rows of {width}")
+    _check(norm_w, "latent norm weight", torch.float32, 1)
+    if norm_w.shape[0] != rank:
+        raise KernelError(f"a norm weight of {norm_w.shape[0]} for a latent of {rank}")
+    if rotary_dim:
+        _check(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.shape[0] != rotary_dim // 2:
+            raise KernelError(f"inv_freq has {inv_freq.shape[0]} entries for a rotation over {rotary_dim}")
+    _check(block_table, "block table", torch.int32, 2)
+    status = library().shiso_latent_store(
+        rows.data_ptr(), ld, _code(rows), _ptr(norm_w), _ptr(inv_freq) if rotary_dim else 0, _ptr(step.positions),
+        _ptr(step.seq_of_token), _ptr(block_table), block_table.shape[1], _ptr(k_cache), tokens, int(rank), width, int(rotary_dim),
+        page_size, float(eps), _stream(),
+    )
+    _done(status, "latent_store", shape=(tokens, width))
+
+
+def rotate_heads(x, out, inv_freq, rotary_dim, step):
+    """``x[T, H, W]`` with the half-split pairs of its first ``rotary_dim`` columns turned by each row's
+    position, into ``out[T, H, W]``; both may be column ranges of wider rows."""
+    act = x.dtype
+    x_ld, x_hs = _heads3(x, "x", act)
+    out_ld, out_hs = _heads3(out, "out", act)
+    if x.shape != out.shape:
+        raise KernelError(f"rows of {tuple(x.shape)} into {tuple(out.shape)}")
+    if rotary_dim:
+        _check(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.shape[0] != rotary_dim // 2:
+            raise KernelError(f"inv_freq has {inv_freq.shape[0]} entries for a rotation over {rotary_dim}")
+    tokens, heads, width = x.shape
+    status = library().shiso_rotate_heads(
+        x.data_ptr(), x_ld, x_hs, out.data_ptr(), out_ld, out_hs, _CODES[act], _ptr(inv_freq) if rotary_dim else 0,
+        _ptr(step.positions), tokens, heads, width, int(rotary_dim), _stream(),
+    )
+    _done(status, "rotate_heads", shape=(tokens, heads, width))
+
+
+def head_linear(x, w, out, gate=None):
+    """A product per head: ``out[t, h] = w[h] x[t, h]`` for ``x[T, H, K]``, ``w[H, N, K]``, ``out[T, H, N]``
+    (x and out may be column ranges); with ``gate[T, H]`` (a column range of rows of x's type) the
+    head's result is multiplied by ``sigmoid(gate[t, h])``.  Float accumulation on CUDA cores."""
+    x_ld, x_hs = _heads3(x, "x", None)
+    out_ld, out_hs = _heads3(out, "out", None)
+    _check(w, "w", None, 3)
+    tokens, heads, k = x.shape
+    n = w.shape[1]
+    if w.shape != (heads, n, k) or out.shape != (tokens, heads, n):
+        raise KernelError(f"x {tuple(x.shape)}, w {tuple(w.shape)} and out {tuple(out.shape)} do not fit")
+    gate_ld = _rows(gate, "gate", x.dtype, heads) if gate is not None else 0
+    status = library().shiso_head_linear(
+        x.data_ptr(), x_ld, x_hs, _code(x), _ptr(w), _code(w), out.data_ptr(), out_ld, out_hs, _code(out),
+        gate.data_ptr() if gate is not None else 0, gate_ld, tokens, heads, n, k, _stream(),
+    )
+    _done(status, "head_linear", shape=(tokens, heads, n, k))
+    return out
+
+
+LATENT_DECODE_SHARE_KEYS = 1024  # a decode step's keys are shared out over CTAs in ranges of about this many ...
+LATENT_MAX_SHARES = 16  # ... up to this many CTAs a (row, head group)
+
+
+def latent_attention(q_lat, rank, k_cache, block_table, page_size, scale, step):
+    """Causal softmax attention of ``q_lat[T, H, W]`` against the cached rows ``k_cache[pages, page_size,
+    1, W]`` of each row's sequence; the values are the first ``rank`` entries of the same rows.
+    Returns ``[T, H, rank]`` in the input type."""
+    _check(q_lat, "q", None, 3)
+    tokens, heads, width = q_lat.shape
+    _paged(k_cache, "latent cache", q_lat.dtype, page_size)
+    if k_cache.shape[2:] != (1, width) or not 0 < rank <= width:
+        raise KernelError(f"a cache of shape {tuple(k_cache.shape)} for queries of {width} and a latent of {rank}")
+    _check(block_table, "block table", torch.int32, 2)
+    out = torch.empty((tokens, heads, rank), dtype=q_lat.dtype, device=q_lat.device)
+    # steps of single tokens at long contexts: a row's keys go to several CTAs (the split depends on the step's shape only)
+    shares, scratch = 1, None
+    if getattr(step, "all_decode", False):
+        context = block_table.shape[1] * page_size
+        shares = max(1, min(LATENT_MAX_SHARES, context // LATENT_DECODE_SHARE_KEYS, _sm_count() // max(1, tokens * -(-heads // 4))))
+        if shares > 1:
+            scratch = torch.empty((tokens * heads * shares * (rank + 2),), dtype=torch.float32, device=q_lat.device)
+    status = library().shiso_latent_attention(
+        _ptr(q_lat), _code(q_lat), _ptr(k_cache), _ptr(block_table), block_table.shape[1], _ptr(step.positions),
+        _ptr(step.seq_of_token), _ptr(out), _ptr(scratch), tokens, heads, int(rank), width, page_size, float(scale), shares, _stream(),
+    )
+    _done(status, "latent_attention", 2 if shares > 1 else 1, shape=(tokens, heads, width))
+    return out
+
+
+# --------------------------------------------------------------------------- mixture of experts
+
+
+def moe_route(logits, top, group_count, group_keep, scale, sigmoid=False, renormalize=False):
+    """For every row of ``logits`` (float32 ``[T, E]``): scores (softmax over all experts, or
+    sigmoids), the ``top`` largest among the experts of the ``group_keep`` best of ``group_count``
+    groups of neighbours (a group's score is its largest), and their weights: the scores (divided
+    by their sum with ``renormalize``) times ``scale``.  Returns ids int32 and weights float32,
+    both ``[T, top]``, best first."""
+    _check(logits, "router logits", torch.float32, 2)
+    tokens, experts = logits.shape
+    ids = torch.empty((tokens, top), dtype=torch.int32, device=logits.device)
+    weights = torch.empty((tokens, top), dtype=torch.float32, device=logits.device)
+    status = library().shiso_moe_route(
+        _ptr(logits), _ptr(ids), _ptr(weights), tokens, experts, int(top), int(group_count), int(group_keep), float(scale),
+        int(bool(sigmoid)), int(bool(renormalize)), _stream(),
+    )
+    _done(status, "moe_route", shape=(tokens, experts, top))
+    return ids, weights
+
+
+def routed_experts(x, ids, weights, gate_up, down, extra=None):
+    """``out[t] = extra[t] + sum_j weights[t, j] * expert_{ids[t, j]}(x[t])`` with gated experts
+    ``down[e] (silu(gate x) * (up x))``, ``gate_up[e] = [gate; up]``: ``x[T, H]``, ``gate_up[E, 2F, H]``,
+    ``down[E, H, F]``.  The (row, choice) pairs are grouped by expert on the device; nothing about the
+    routing reaches the host."""
+    _check(x, "x", None, 2)
+    _check(ids, "expert ids", torch.int32, 2)
+    _check(weights, "expert weights", torch.float32, 2)
+    _check(gate_up, "gate/up matrices", None, 3)
+    _check(down, "down matrices", gate_up.dtype, 3)
+    tokens, hidden = x.shape
+    experts, two_ff, _ = gate_up.shape
+    top = ids.shape[1]
+    if ids.shape != (tokens, top) or weights.shape != ids.shape or gate_up.shape[2] != hidden or down.shape != (experts, hidden, two_ff // 2):
+        raise KernelError("ids, weights or expert matrices of the wrong shape")
+    if extra is not None:
+        _check(extra, "extra", x.dtype, 2)
+        if extra.shape != x.shape:
+            raise KernelError(f"extra rows of {tuple(extra.shape)} beside {tuple(x.shape)}")
+    ff, total = two_ff // 2, tokens * top
+    ints = torch.empty((experts + 3 * total,), dtype=torch.int32, device=x.device)
+    mid = torch.empty((total, ff), dtype=x.dtype, device=x.device)
+    y = torch.empty((total, hidden), dtype=torch.float32, device=x.device)
+    out = torch.empty_like(x)
+    status = library().shiso_routed_experts(
+        _ptr(x), _code(x), _ptr(ids), _ptr(weights), _ptr(gate_up), _ptr(down), _code(gate_up), _ptr(extra), _ptr(out), _ptr(ints),
+        _ptr(mid), _ptr(y), tokens, hidden, ff, experts, top, _stream(),
+    )
+    _done(status, "routed_experts", 6, shape=(tokens, top, experts, ff, hidden))
     return out
 
 
