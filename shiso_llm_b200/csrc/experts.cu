@@ -6,7 +6,8 @@
 // gather[m] / gather_div).  CUDA cores, float accumulation, a tile of 32 rows x 64 outputs per CTA
 // and 32 columns of K per pass; an output's sum runs over K in order, whatever else is in its tile, so
 // a row's result does not depend on the batch.  Epilogues: none; times sigmoid(gate[m, b]); or, for
-// a matrix that stacks gate over up rows, silu(gate) * up.
+// a matrix that stacks gate over up rows, silu(gate) * up.  bfloat16 inputs whose strides allow
+// 16-byte copies take tile_gemm_mma_kernel instead: the same tiles on the tensor cores.
 //
 // Routing: moe_route_kernel (a warp per row: scores, group-limited choice of the top experts,
 // weights), moe_count / moe_place (rows grouped by expert with two passes of integer atomics:
@@ -130,9 +131,180 @@ __global__ void __launch_bounds__(256) tile_gemm_kernel(const TileGemmArgs a) {
     }
 }
 
+// ---- the same products on the tensor cores (bfloat16 inputs) -------------------------------
+// 64 rows x 128 outputs per CTA and 32 columns of K per stage, eight warps of 32 x 32 outputs,
+// mma.sync m16n8k16 with float accumulators; rows (gathered through the same index) and matrix rows
+// come by 16-byte cp.async into three stages of padded shared-memory rows that ldmatrix reads without
+// bank conflicts.  With a stacked gate/up matrix both halves are accumulated and the epilogue
+// writes silu(gate) * up.  Needs K, the row strides and the batch strides to be multiples of 8.
+#define TM_BM 64
+#define TM_BN 128
+#define TM_BK 32
+#define TM_ROW 80  // bytes of a padded shared-memory row: 32 bfloat16 + 16 bytes
+#define TM_STAGES 3
+
+__device__ __forceinline__ uint32_t tm_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void tm_cp16(void* dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(tm_smem(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tm_ldmatrix(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void tm_mma(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <typename OT, bool GLU>
+__global__ void __launch_bounds__(256) tile_gemm_mma_kernel(const TileGemmArgs a) {
+    extern __shared__ __align__(16) uint8_t tm_sm[];
+    uint8_t* xs = tm_sm;                                  // [TM_STAGES][TM_BM][TM_ROW]
+    uint8_t* ws = xs + TM_STAGES * TM_BM * TM_ROW;        // [TM_STAGES][(GLU ? 2 : 1) * TM_BN][TM_ROW]
+    constexpr int WROWS = (GLU ? 2 : 1) * TM_BN;
+    __shared__ int s_batch, s_row0, s_rows;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    pdl_wait();
+    int batch, row0, row_end;
+    if (a.counts) {
+        if (tid == 0) {
+            int tile = blockIdx.y, start = 0, b = 0, found = -1;
+            for (; b < a.batches; ++b) {
+                const int c = a.counts[b], tiles = (c + TM_BM - 1) / TM_BM;
+                if (tile < tiles) { found = b; break; }
+                tile -= tiles;
+                start += c;
+            }
+            s_batch = found;
+            s_row0 = start + tile * TM_BM;
+            s_rows = found >= 0 ? start + a.counts[found] : 0;
+        }
+        __syncthreads();
+        batch = s_batch, row0 = s_row0, row_end = s_rows;
+        if (batch < 0) return;
+    } else {
+        batch = blockIdx.z, row0 = blockIdx.y * TM_BM, row_end = a.M;
+        if (row0 >= row_end) return;
+    }
+    const int n0 = blockIdx.x * TM_BN;
+    const __nv_bfloat16* x = (const __nv_bfloat16*)a.x + (size_t)batch * a.x_bs;
+    const __nv_bfloat16* w = (const __nv_bfloat16*)a.w + (size_t)batch * a.w_bs;
+    // this thread's copies: one 16-byte piece of an input row, WROWS / 64 pieces of matrix rows
+    const int xr = tid >> 2, piece = tid & 3;
+    const __nv_bfloat16* xsrc = nullptr;
+    if (row0 + xr < row_end) {
+        const int m = row0 + xr;
+        xsrc = x + (size_t)(a.gather ? a.gather[m] / a.gather_div : m) * a.x_ld;
+    }
+    auto load = [&](int k0, int stage) {
+        const int k = k0 + piece * 8;
+        tm_cp16(xs + (stage * TM_BM + xr) * TM_ROW + piece * 16, xsrc ? xsrc + k : x, xsrc != nullptr && k < a.K);
+#pragma unroll
+        for (int i = 0; i < WROWS / 64; ++i) {
+            const int r = xr + 64 * i;               // row of the stage: gate rows, then up rows
+            const int half = r / TM_BN, n = n0 + r % TM_BN;
+            const bool ok = n < a.N && k < a.K;
+            tm_cp16(ws + (stage * WROWS + r) * TM_ROW + piece * 16, ok ? w + ((size_t)half * a.N + n) * a.K + k : w, ok);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    const int wm = warp >> 2, wn = warp & 3;
+    float acc[2][4][4] = {}, acc2[GLU ? 2 : 1][4][4] = {};
+    const int steps = (a.K + TM_BK - 1) / TM_BK;
+    load(0, 0);
+    if (steps > 1) load(TM_BK, 1);
+    else asm volatile("cp.async.commit_group;" ::: "memory");
+    for (int s = 0; s < steps; ++s) {
+        const int stage = s % TM_STAGES;
+        if (s + 2 < steps) load((s + 2) * TM_BK, (s + 2) % TM_STAGES);  // the stage that was read an iteration ago
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 2;" ::: "memory");
+        __syncthreads();
+        const uint8_t* xt = xs + stage * TM_BM * TM_ROW;
+        const uint8_t* wt = ws + stage * WROWS * TM_ROW;
+#pragma unroll
+        for (int kk = 0; kk < TM_BK / 16; ++kk) {
+            uint32_t af[2][4];
+#pragma unroll
+            for (int mi = 0; mi < 2; ++mi) {
+                const int r = wm * 32 + mi * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                const int col = kk * 16 + (lane >> 4) * 8;
+                tm_ldmatrix(tm_smem(xt + r * TM_ROW + col * 2), af[mi][0], af[mi][1], af[mi][2], af[mi][3]);
+            }
+#pragma unroll
+            for (int nj = 0; nj < 4; nj += 2) {
+                const int r = wn * 32 + nj * 8 + (lane & 7) + (lane >> 4) * 8;
+                const int col = kk * 16 + ((lane >> 3) & 1) * 8;
+                uint32_t b0, b1, b2, b3;
+                tm_ldmatrix(tm_smem(wt + r * TM_ROW + col * 2), b0, b1, b2, b3);
+#pragma unroll
+                for (int mi = 0; mi < 2; ++mi) {
+                    tm_mma(acc[mi][nj], af[mi], b0, b1);
+                    tm_mma(acc[mi][nj + 1], af[mi], b2, b3);
+                }
+                if (GLU) {
+                    tm_ldmatrix(tm_smem(wt + (TM_BN + r) * TM_ROW + col * 2), b0, b1, b2, b3);
+#pragma unroll
+                    for (int mi = 0; mi < 2; ++mi) {
+                        tm_mma(acc2[mi][nj], af[mi], b0, b1);
+                        tm_mma(acc2[mi][nj + 1], af[mi], b2, b3);
+                    }
+                }
+            }
+        }
+        __syncthreads();
+    }
+    pdl_trigger();
+    OT* out = (OT*)a.out + (size_t)batch * a.out_bs;
+    const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+    for (int mi = 0; mi < 2; ++mi) {
+#pragma unroll
+        for (int hrow = 0; hrow < 2; ++hrow) {
+            const int m = row0 + wm * 32 + mi * 16 + g + hrow * 8;
+            if (m >= row_end) continue;
+            float scale = 1.0f;
+            if (a.gate) scale = 1.0f / (1.0f + expf(-to_f32(((const __nv_bfloat16*)a.gate)[(size_t)m * a.gate_ld + batch])));
+#pragma unroll
+            for (int nj = 0; nj < 4; ++nj) {
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int n = n0 + wn * 32 + nj * 8 + t4 * 2 + e;
+                    if (n >= a.N) continue;
+                    float v = acc[mi][nj][hrow * 2 + e];
+                    if (GLU) v = v / (1.0f + expf(-v)) * acc2[mi][nj][hrow * 2 + e];
+                    out[(size_t)m * a.out_ld + n] = from_f32<OT>(v * scale);
+                }
+            }
+        }
+    }
+}
+
+template <typename OT, bool GLU>
+static int launch_tile_gemm_mma(const TileGemmArgs& a, int rows_upper, int extra_tiles, int z, cudaStream_t stream) {
+    const dim3 grid((a.N + TM_BN - 1) / TM_BN, (rows_upper + TM_BM - 1) / TM_BM + extra_tiles, z);
+    const size_t smem = (size_t)TM_STAGES * (TM_BM + (GLU ? 2 : 1) * TM_BN) * TM_ROW;
+    auto kern = tile_gemm_mma_kernel<OT, GLU>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    launch_kernel(kern, grid, dim3(256), smem, stream, a);
+    return launch_status();
+}
+
+static bool tile_gemm_mma_fits(const TileGemmArgs& a, int x_dtype, int w_dtype) {
+    return x_dtype == SHISO_BF16 && w_dtype == SHISO_BF16 && a.K % 8 == 0 && a.x_ld % 8 == 0 && a.x_bs % 8 == 0 && a.w_bs % 8 == 0 &&
+           (((uintptr_t)a.x | (uintptr_t)a.w) & 15) == 0;
+}
+
 template <bool GLU>
-static int launch_tile_gemm(const TileGemmArgs& a, int x_dtype, int w_dtype, int out_dtype, int row_tiles, int z, cudaStream_t stream) {
-    const dim3 grid((a.N + TG_BN - 1) / TG_BN, row_tiles, z);
+static int launch_tile_gemm(const TileGemmArgs& a, int x_dtype, int w_dtype, int out_dtype, int rows_upper, int extra_tiles, int z,
+                            cudaStream_t stream) {
+    // rows_upper rows in all; with rows grouped by batch, every batch may end in a tile that is not full (extra_tiles)
+    if (tile_gemm_mma_fits(a, x_dtype, w_dtype)) {
+        if (out_dtype == SHISO_BF16) return launch_tile_gemm_mma<__nv_bfloat16, GLU>(a, rows_upper, extra_tiles, z, stream);
+        if (out_dtype == SHISO_F32) return launch_tile_gemm_mma<float, GLU>(a, rows_upper, extra_tiles, z, stream);
+    }
+    const dim3 grid((a.N + TG_BN - 1) / TG_BN, (rows_upper + TG_BM - 1) / TG_BM + extra_tiles, z);
     typedef __nv_bfloat16 bf;
 #define TG_GO(XT, WT, OT)                                                                 \
     {                                                                                     \
@@ -155,7 +327,7 @@ SHISO_API int shiso_head_linear(const void* x, long long x_ld, long long x_hs, i
     if (tokens <= 0 || heads <= 0 || n <= 0) return SHISO_OK;
     if (k <= 0 || heads > 65535) return SHISO_ERR_SHAPE;
     TileGemmArgs a = {x, x_ld, x_hs, nullptr, 1, w, (long long)n * k, out, out_ld, out_hs, nullptr, gate, gate_ld, tokens, n, k, heads};
-    return launch_tile_gemm<false>(a, x_dtype, w_dtype, out_dtype, (tokens + TG_BM - 1) / TG_BM, heads, stream);
+    return launch_tile_gemm<false>(a, x_dtype, w_dtype, out_dtype, tokens, 0, heads, stream);
 }
 
 // --------------------------------------------------------------------------- routing
@@ -313,12 +485,11 @@ SHISO_API int shiso_routed_experts(const void* x, int act_dtype, const int* ids,
                   total, experts);
     int status = launch_status();
     if (status) return status;
-    const int row_tiles = (total + TG_BM - 1) / TG_BM + experts;  // every expert may end in a tile that is not full
     TileGemmArgs up = {x, hidden, 0, source, top, gate_up, (long long)2 * ff * hidden, mid, ff, 0, counts, nullptr, 0, total, ff, hidden, experts};
-    status = launch_tile_gemm<true>(up, act_dtype, w_dtype, act_dtype, row_tiles, 1, stream);
+    status = launch_tile_gemm<true>(up, act_dtype, w_dtype, act_dtype, total, experts, 1, stream);
     if (status) return status;
     TileGemmArgs dn = {mid, ff, 0, nullptr, 1, down, (long long)hidden * ff, y, hidden, 0, counts, nullptr, 0, total, hidden, ff, experts};
-    status = launch_tile_gemm<false>(dn, act_dtype, w_dtype, SHISO_F32, row_tiles, 1, stream);
+    status = launch_tile_gemm<false>(dn, act_dtype, w_dtype, SHISO_F32, total, experts, 1, stream);
     if (status) return status;
     const unsigned blocks = ceil_div_u((long long)tokens * hidden, 256);
     if (act_dtype == SHISO_F32)

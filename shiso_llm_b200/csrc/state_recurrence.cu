@@ -9,10 +9,11 @@
 // a group (head h reads group h / (heads / groups)); silu may be applied to q, k and v on load.
 //
 // One CTA walks the rows of one (head, sequence, range of value columns) in order.  A warp holds 8
-// columns; the key rows of a column are dealt to 4 lanes (row n to lane n % 4), so a lane keeps
-// dim / 4 state values in registers and an output is a sum over a lane's rows followed by two
-// shuffles: what is added to what, and in which order, depends on dim only - never on how the
-// sequence was cut into steps, on the batch, or on how many columns a CTA was given.  Rows are
+// columns; the key rows of a column are dealt to 4 lanes in runs of four (rows 16 j + 4 lane ..
+// + 3 to a lane, so that a lane reads its keys and queries as 16-byte words of shared memory); a
+// lane keeps dim / 4 state values in registers and an output is a sum over a lane's rows followed
+// by two shuffles: what is added to what, and in which order, depends on dim only - never on how
+// the sequence was cut into steps, on the batch, or on how many columns a CTA was given.  Rows are
 // staged in shared memory sixteen at a time (activations and the two exponentials applied once, on
 // the way in).  Outputs are float rows [T, heads * vdim]: the norm and gate that follow them are a
 // row kernel's.
@@ -40,10 +41,11 @@ __global__ void __launch_bounds__(256) state_recurrence_kernel(const StateRecurr
     const int part = lane & 3, local = warp * 8 + (lane >> 2), col = col0 + local;
     const bool live = col < a.vdim;
     const int dim = a.dim, vdim = a.vdim, g = h / (a.heads / a.groups);
-    extern __shared__ float sm[];
-    float* sq = sm;                         // [SR_TOKENS][dim]
-    float* sk = sq + SR_TOKENS * dim;       // [SR_TOKENS][dim]
-    float* sv = sk + SR_TOKENS * dim;       // [SR_TOKENS][cols]
+    constexpr int DP = 4 * RPT;             // key rows with padding (zeros: their state stays zero)
+    extern __shared__ __align__(16) float sm[];
+    float* sq = sm;                         // [SR_TOKENS][DP]
+    float* sk = sq + SR_TOKENS * DP;        // [SR_TOKENS][DP]
+    float* sv = sk + SR_TOKENS * DP;        // [SR_TOKENS][cols]
     float* sa = sv + SR_TOKENS * a.cols;    // [SR_TOKENS]
     float* sb = sa + SR_TOKENS;             // [SR_TOKENS]
     const float skip = a.skip ? a.skip[h] : 0.0f;
@@ -57,7 +59,7 @@ __global__ void __launch_bounds__(256) state_recurrence_kernel(const StateRecurr
     float S[RPT];
 #pragma unroll
     for (int r = 0; r < RPT; ++r) {
-        const int row = part + 4 * r;
+        const int row = (r >> 2) * 16 + part * 4 + (r & 3);
         S[r] = (live && row < dim) ? slot[(size_t)row * vdim + col] : 0.0f;
     }
     const AT* qp = (const AT*)a.q + (size_t)g * dim;
@@ -68,12 +70,15 @@ __global__ void __launch_bounds__(256) state_recurrence_kernel(const StateRecurr
     for (int base = 0; base < n; base += SR_TOKENS) {
         const int count = min(SR_TOKENS, n - base);
         const size_t row0 = (size_t)(first + base);
-        for (int i = threadIdx.x; i < count * dim; i += blockDim.x) {
-            const int t = i / dim, c = i - t * dim;
-            float qv = to_f32(qp[(row0 + t) * a.q_ld + c]), kv = to_f32(kp[(row0 + t) * a.k_ld + c]);
-            if (a.silu) qv = sr_silu(qv), kv = sr_silu(kv);
-            sq[t * dim + c] = qv;
-            sk[t * dim + c] = kv;
+        for (int i = threadIdx.x; i < count * DP; i += blockDim.x) {
+            const int t = i / DP, c = i - t * DP;
+            float qv = 0.0f, kv = 0.0f;
+            if (c < dim) {
+                qv = to_f32(qp[(row0 + t) * a.q_ld + c]), kv = to_f32(kp[(row0 + t) * a.k_ld + c]);
+                if (a.silu) qv = sr_silu(qv), kv = sr_silu(kv);
+            }
+            sq[i] = qv;
+            sk[i] = kv;
         }
         for (int i = threadIdx.x; i < count * a.cols; i += blockDim.x) {
             const int t = i / a.cols, c = i - t * a.cols;
@@ -91,26 +96,36 @@ __global__ void __launch_bounds__(256) state_recurrence_kernel(const StateRecurr
         }
         __syncthreads();
         for (int t = 0; t < count; ++t) {
-            const float* qt = sq + t * dim + part;
-            const float* kt = sk + t * dim + part;
+            const float4* qt = reinterpret_cast<const float4*>(sq + t * DP) + part;
+            const float4* kt = reinterpret_cast<const float4*>(sk + t * DP) + part;
             const float vt = sv[t * a.cols + local];
             float acc = 0.0f;
             if (dtp) {
                 const float decay = sa[t], bv = sb[t] * vt;
 #pragma unroll
-                for (int r = 0; r < RPT; ++r) {
-                    if (part + 4 * r < dim) {
-                        S[r] = fmaf(decay, S[r], kt[4 * r] * bv);
-                        acc = fmaf(S[r], qt[4 * r], acc);
-                    }
+                for (int j = 0; j < RPT / 4; ++j) {
+                    const float4 k4 = kt[4 * j], q4 = qt[4 * j];
+                    S[4 * j] = fmaf(decay, S[4 * j], k4.x * bv);
+                    S[4 * j + 1] = fmaf(decay, S[4 * j + 1], k4.y * bv);
+                    S[4 * j + 2] = fmaf(decay, S[4 * j + 2], k4.z * bv);
+                    S[4 * j + 3] = fmaf(decay, S[4 * j + 3], k4.w * bv);
+                    acc = fmaf(S[4 * j], q4.x, acc);
+                    acc = fmaf(S[4 * j + 1], q4.y, acc);
+                    acc = fmaf(S[4 * j + 2], q4.z, acc);
+                    acc = fmaf(S[4 * j + 3], q4.w, acc);
                 }
             } else {
 #pragma unroll
-                for (int r = 0; r < RPT; ++r) {
-                    if (part + 4 * r < dim) {
-                        S[r] = fmaf(kt[4 * r], vt, fmaf(-loss, S[r], S[r]));
-                        acc = fmaf(S[r], qt[4 * r], acc);
-                    }
+                for (int j = 0; j < RPT / 4; ++j) {
+                    const float4 k4 = kt[4 * j], q4 = qt[4 * j];
+                    S[4 * j] = fmaf(k4.x, vt, fmaf(-loss, S[4 * j], S[4 * j]));
+                    S[4 * j + 1] = fmaf(k4.y, vt, fmaf(-loss, S[4 * j + 1], S[4 * j + 1]));
+                    S[4 * j + 2] = fmaf(k4.z, vt, fmaf(-loss, S[4 * j + 2], S[4 * j + 2]));
+                    S[4 * j + 3] = fmaf(k4.w, vt, fmaf(-loss, S[4 * j + 3], S[4 * j + 3]));
+                    acc = fmaf(S[4 * j], q4.x, acc);
+                    acc = fmaf(S[4 * j + 1], q4.y, acc);
+                    acc = fmaf(S[4 * j + 2], q4.z, acc);
+                    acc = fmaf(S[4 * j + 3], q4.w, acc);
                 }
             }
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
@@ -122,30 +137,31 @@ __global__ void __launch_bounds__(256) state_recurrence_kernel(const StateRecurr
     pdl_trigger();
 #pragma unroll
     for (int r = 0; r < RPT; ++r) {
-        const int row = part + 4 * r;
+        const int row = (r >> 2) * 16 + part * 4 + (r & 3);
         if (live && row < dim) slot[(size_t)row * vdim + col] = S[r];
     }
 }
 
 template <typename AT>
 static int launch_state_recurrence(const StateRecurrenceArgs& a, int num_seqs, int sm_count, cudaStream_t stream) {
-    // value columns per CTA: as few as keeps every SM busy, in steps a warp's 8 columns allow
+    // value columns per CTA: fewer while SMs would stay idle, but at least 32 (every CTA stages and
+    // activates its head's keys and queries itself, so narrow CTAs repeat that work), or what the head has
     int cols = 64;
-    while (cols > 8 && (long long)a.heads * num_seqs * ((a.vdim + cols - 1) / cols) < sm_count) cols /= 2;
+    while (cols > 32 && (long long)a.heads * num_seqs * ((a.vdim + cols - 1) / cols) < sm_count) cols /= 2;
     while (cols > 8 && cols / 2 >= a.vdim) cols /= 2;
     StateRecurrenceArgs args = a;
     args.cols = cols;
     const dim3 grid(a.heads, num_seqs, (a.vdim + cols - 1) / cols), block(cols * 4);
-    const size_t smem = (size_t)(2 * SR_TOKENS * a.dim + SR_TOKENS * cols + 2 * SR_TOKENS) * sizeof(float);
-    const int rpt = (a.dim + 3) / 4;
+    const int rpt = (a.dim + 15) / 16 * 4;  // key rows in runs of 16: four to each of a column's four lanes
 #define SR_CASE(R)                                                                                                   \
     if (rpt <= R) {                                                                                                  \
+        const size_t smem = (size_t)(2 * SR_TOKENS * 4 * R + SR_TOKENS * cols + 2 * SR_TOKENS) * sizeof(float);      \
         auto kern = state_recurrence_kernel<AT, R>;                                                                  \
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
         launch_kernel(kern, grid, block, smem, stream, args);                                                        \
         return launch_status();                                                                                      \
     }
-    SR_CASE(2) SR_CASE(4) SR_CASE(8) SR_CASE(16) SR_CASE(32) SR_CASE(64)
+    SR_CASE(4) SR_CASE(8) SR_CASE(16) SR_CASE(32) SR_CASE(64)
 #undef SR_CASE
     return SHISO_ERR_SHAPE;
 }

@@ -109,7 +109,23 @@ def library_path(create: bool = True) -> str:
     return build(d)
 
 
+def _object_hash(src: str) -> str:
+    """What an object file depends on: its source, every header, the flags."""
+    h = hashlib.sha256()
+    for path in [src] + _headers():
+        h.update(os.path.basename(path).encode())
+        with open(path, "rb") as f:
+            h.update(f.read())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()[:20]
+
+
 def _compile_one(nvcc: str, src: str, obj: str, verbose: bool) -> str:
+    """Compiles one file, unless the object beside its stamp was built from the same source,
+    headers and flags (a change to one kernel file then rebuilds that file only)."""
+    stamp, want = obj + ".hash", _object_hash(src)
+    if not verbose and os.path.isfile(obj) and os.path.isfile(stamp) and open(stamp).read().strip() == want:
+        return ""
     cmd = [nvcc, *NVCC_FLAGS, "-I", CSRC, "-c", src, "-o", obj]
     if verbose:
         cmd.insert(1, "-Xptxas")
@@ -117,6 +133,8 @@ def _compile_one(nvcc: str, src: str, obj: str, verbose: bool) -> str:
     proc = subprocess.run(cmd, capture_output=True, text=True)
     if proc.returncode != 0:
         raise BuildError(f"nvcc failed on {os.path.basename(src)}:\n{proc.stdout}\n{proc.stderr}")
+    with open(stamp, "w") as f:
+        f.write(want + "\n")
     return proc.stderr
 
 
@@ -134,7 +152,8 @@ def build(directory: str | None = None, verbose: bool = False) -> str:
         futures = {pool.submit(_compile_one, nvcc, s, o, verbose): s for s, o in zip(srcs, objs)}
         for fut in concurrent.futures.as_completed(futures):
             log.append(fut.result())
-            _say(f"  compiled {os.path.basename(futures[fut])} ({time.time() - started:.0f} s)")
+            if log[-1] is not None:
+                _say(f"  compiled {os.path.basename(futures[fut])} ({time.time() - started:.0f} s)")
     tmp_lib = os.path.join(d, f".{LIB_NAME}.{os.getpid()}")
     link = [nvcc, "-shared", "-o", tmp_lib, *objs, "-gencode", "arch=compute_100a,code=sm_100a"]
     proc = subprocess.run(link, capture_output=True, text=True)
