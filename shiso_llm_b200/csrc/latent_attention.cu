@@ -224,3 +224,241 @@ SHISO_API int shiso_latent_attention(const void* q, int act_dtype, const void* c
                                                       heads, rank, width, page_size, scale, shares, stream);
     return SHISO_ERR_DTYPE;
 }
+
+// --------------------------------------------------------------------------- prompt portions on the tensor cores
+//
+// bfloat16 steps with prompt portions: a CTA takes 16 query rows of one sequence and up to eight
+// heads, a warp a head.  All heads score against the same cached rows, so a tile of 32 keys is brought
+// into shared memory once (16-byte cp.async through the block table, two stages) and read by every
+// warp: S = Q K^T by mma.sync m16n8k16 over the whole row width, a base-2 online softmax in
+// registers, P rounded to bfloat16 as the A operand of O += P V, where V is the first `rank`
+// columns of the very same shared-memory tile, read transposed by ldmatrix.  Needs the row width
+// and the rank to be multiples of 16 and a rank of at most 256 (a warp keeps 16 x rank sums).
+
+struct LatentPrefillArgs {
+    const __nv_bfloat16* q;
+    const __nv_bfloat16* cache;
+    const int* block_table;
+    int table_width;
+    const int *q_start, *start_pos;
+    __nv_bfloat16* out;
+    int num_seqs, heads, rank, width, page_size;
+    float scale_log2;
+};
+
+__device__ __forceinline__ uint32_t lp_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void lp_cp16(void* dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(lp_smem(dst)), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void lp_ldmatrix(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void lp_ldmatrix_trans(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void lp_mma(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t lp_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+#define LP_BM 16
+#define LP_BN 32
+
+// RT: 8-column tiles of the result a warp keeps (rank <= 8 RT).  HG: heads (warps) per CTA.
+template <int RT, int HG>
+__global__ void __launch_bounds__(HG * 32) latent_prefill_mma_kernel(const LatentPrefillArgs a) {
+    extern __shared__ __align__(16) uint8_t lp_sm[];
+    const int WB = a.width * 2 + 16;  // bytes of a padded shared-memory row
+    uint8_t* q_s = lp_sm;                       // [HG][LP_BM][WB]
+    uint8_t* k_s = q_s + HG * LP_BM * WB;       // [2][LP_BN][WB]
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
+    pdl_wait();
+    int tile = blockIdx.y, s = 0, len = 0;
+    for (; s < a.num_seqs; ++s) {
+        len = a.q_start[s + 1] - a.q_start[s];
+        const int nt = (len + LP_BM - 1) / LP_BM;
+        if (tile < nt) break;
+        tile -= nt;
+    }
+    if (s == a.num_seqs) return;
+    const int first_token = a.q_start[s] + tile * LP_BM;
+    const int rows = min(LP_BM, len - tile * LP_BM);
+    const int first_pos = a.start_pos[s] + tile * LP_BM, last_pos = first_pos + rows - 1;
+    const int* table = a.block_table + (size_t)s * a.table_width;
+    const int head0 = blockIdx.x * HG, head = head0 + warp;
+    const bool active = head < a.heads;
+    const int chunks = a.width / 8, rt = a.rank / 8;
+
+    for (int c = tid; c < HG * LP_BM * chunks; c += HG * 32) {
+        const int hh = c / (LP_BM * chunks), rem = c - hh * (LP_BM * chunks), r = rem / chunks, ch = rem - r * chunks;
+        const bool valid = r < rows && head0 + hh < a.heads;
+        const __nv_bfloat16* src = a.q + ((size_t)(first_token + r) * a.heads + head0 + hh) * a.width + ch * 8;
+        lp_cp16(q_s + (hh * LP_BM + r) * WB + ch * 16, valid ? src : a.q, valid);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    auto load_keys = [&](int kt, int stage) {
+        for (int c = tid; c < LP_BN * chunks; c += HG * 32) {
+            const int r = c / chunks, ch = c - r * chunks;
+            const int key = kt * LP_BN + r;
+            const bool valid = key <= last_pos;
+            size_t row = 0;
+            if (valid) row = (size_t)table[key / a.page_size] * a.page_size + key % a.page_size;
+            lp_cp16(k_s + (stage * LP_BN + r) * WB + ch * 16, a.cache + row * a.width + ch * 8, valid);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    load_keys(0, 0);
+
+    float o_acc[RT][4];
+#pragma unroll
+    for (int i = 0; i < RT; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.0f;
+    float row_max[2] = {-INFINITY, -INFINITY}, row_sum[2] = {0.0f, 0.0f};
+    const int my_pos[2] = {first_pos + g, first_pos + g + 8};
+    const int n_tiles = last_pos / LP_BN + 1;
+    for (int kt = 0; kt < n_tiles; ++kt) {
+        const int stage = kt & 1;
+        if (kt + 1 < n_tiles) load_keys(kt + 1, stage ^ 1);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        __syncthreads();
+        const uint8_t* ks = k_s + stage * LP_BN * WB;
+        if (active && kt * LP_BN <= first_pos + LP_BM - 1) {
+            float s_acc[LP_BN / 8][4];
+#pragma unroll
+            for (int j = 0; j < LP_BN / 8; ++j) s_acc[j][0] = s_acc[j][1] = s_acc[j][2] = s_acc[j][3] = 0.0f;
+            for (int kk = 0; kk < a.width / 16; ++kk) {
+                uint32_t af[4];
+                {
+                    const int r = warp * LP_BM + (lane & 7) + ((lane >> 3) & 1) * 8;
+                    const int col = kk * 16 + (lane >> 4) * 8;
+                    lp_ldmatrix(lp_smem(q_s + r * WB + col * 2), af[0], af[1], af[2], af[3]);
+                }
+#pragma unroll
+                for (int j = 0; j < LP_BN / 8; j += 2) {
+                    const int r = j * 8 + (lane & 7) + (lane >> 4) * 8;
+                    const int col = kk * 16 + ((lane >> 3) & 1) * 8;
+                    uint32_t b0, b1, b2, b3;
+                    lp_ldmatrix(lp_smem(ks + r * WB + col * 2), b0, b1, b2, b3);
+                    lp_mma(s_acc[j], af, b0, b1);
+                    lp_mma(s_acc[j + 1], af, b2, b3);
+                }
+            }
+            const int key0 = kt * LP_BN;
+            float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int j = 0; j < LP_BN / 8; ++j) {
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key0 + j * 8 + t4 * 2 + (e & 1);
+                    const float v = key <= my_pos[e >> 1] ? s_acc[j][e] * a.scale_log2 : -INFINITY;
+                    s_acc[j][e] = v;
+                    tile_max[e >> 1] = fmaxf(tile_max[e >> 1], v);
+                }
+            }
+            float correction[2], use_max[2];
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                float m = tile_max[r];
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 1));
+                m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, 2));
+                const float new_max = fmaxf(row_max[r], m);
+                use_max[r] = new_max == -INFINITY ? 0.0f : new_max;
+                correction[r] = exp2f(row_max[r] - use_max[r]);
+                row_max[r] = new_max;
+            }
+            float tile_sum[2] = {0.0f, 0.0f};
+            uint32_t p_frag[LP_BN / 16][4];
+#pragma unroll
+            for (int j = 0; j < LP_BN / 8; ++j) {
+                float p[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    p[e] = exp2f(s_acc[j][e] - use_max[e >> 1]);
+                    tile_sum[e >> 1] += p[e];
+                }
+                p_frag[j >> 1][(j & 1) * 2 + 0] = lp_pack(p[0], p[1]);
+                p_frag[j >> 1][(j & 1) * 2 + 1] = lp_pack(p[2], p[3]);
+            }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) row_sum[r] = row_sum[r] * correction[r] + tile_sum[r];
+#pragma unroll
+            for (int i = 0; i < RT; ++i) {
+                o_acc[i][0] *= correction[0];
+                o_acc[i][1] *= correction[0];
+                o_acc[i][2] *= correction[1];
+                o_acc[i][3] *= correction[1];
+            }
+#pragma unroll
+            for (int kb = 0; kb < LP_BN / 16; ++kb) {
+#pragma unroll
+                for (int dn = 0; dn < RT; dn += 2) {
+                    if (dn < rt) {
+                        const int r = kb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+                        const int col = (dn + (lane >> 4)) * 8;
+                        uint32_t b0, b1, b2, b3;
+                        lp_ldmatrix_trans(lp_smem(ks + r * WB + col * 2), b0, b1, b2, b3);
+                        lp_mma(o_acc[dn], p_frag[kb], b0, b1);
+                        lp_mma(o_acc[dn + 1], p_frag[kb], b2, b3);
+                    }
+                }
+            }
+        }
+        __syncthreads();  // the stage is refilled by the next iteration's copies
+    }
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    pdl_trigger();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float sum = row_sum[r];
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        row_sum[r] = sum > 0.0f ? 1.0f / sum : 0.0f;
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = g + r * 8;
+        if (active && row < rows) {
+            __nv_bfloat16* dst = a.out + ((size_t)(first_token + row) * a.heads + head) * a.rank;
+#pragma unroll
+            for (int i = 0; i < RT; ++i)
+                if (i < rt) *reinterpret_cast<uint32_t*>(dst + i * 8 + t4 * 2) = lp_pack(o_acc[i][r * 2] * row_sum[r], o_acc[i][r * 2 + 1] * row_sum[r]);
+        }
+    }
+}
+
+template <int RT, int HG>
+static int launch_latent_prefill(const LatentPrefillArgs& a, int tiles, cudaStream_t stream) {
+    const size_t smem = (size_t)(HG * LP_BM + 2 * LP_BN) * (a.width * 2 + 16);
+    if (smem > 200 * 1024) return SHISO_ERR_SHAPE;
+    auto kern = latent_prefill_mma_kernel<RT, HG>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    launch_kernel(kern, dim3((a.heads + HG - 1) / HG, tiles), dim3(HG * 32), smem, stream, a);
+    return launch_status();
+}
+
+SHISO_API int shiso_latent_prefill_supported(int rank, int width) {
+    return rank > 0 && rank % 16 == 0 && rank <= 256 && width % 16 == 0 && width >= rank &&
+           (size_t)(8 * LP_BM + 2 * LP_BN) * (width * 2 + 16) <= 200 * 1024;
+}
+
+// q [T, H, width], out [T, H, rank], both bfloat16; `tiles`: an upper bound of the 16-row tiles of all sequences.
+SHISO_API int shiso_latent_prefill(const void* q, const void* cache, const int* block_table, int table_width, const int* q_start,
+                                   const int* start_pos, void* out, int num_seqs, int tiles, int heads, int rank, int width,
+                                   int page_size, float scale, cudaStream_t stream) {
+    if (tiles <= 0 || heads <= 0 || num_seqs <= 0) return SHISO_OK;
+    if (!shiso_latent_prefill_supported(rank, width) || page_size <= 0) return SHISO_ERR_SHAPE;
+    if ((((uintptr_t)q | (uintptr_t)cache | (uintptr_t)out) & 15) != 0) return SHISO_ERR_ALIGN;
+    LatentPrefillArgs a = {(const __nv_bfloat16*)q, (const __nv_bfloat16*)cache, block_table, table_width, q_start, start_pos,
+                           (__nv_bfloat16*)out, num_seqs, heads, rank, width, page_size, scale * 1.4426950408889634f};
+    if (rank <= 128) return heads > 4 ? launch_latent_prefill<16, 8>(a, tiles, stream) : launch_latent_prefill<16, 4>(a, tiles, stream);
+    return heads > 4 ? launch_latent_prefill<32, 8>(a, tiles, stream) : launch_latent_prefill<32, 4>(a, tiles, stream);
+}

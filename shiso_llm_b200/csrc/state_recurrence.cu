@@ -15,7 +15,8 @@
 // by two shuffles: what is added to what, and in which order, depends on dim only - never on how
 // the sequence was cut into steps, on the batch, or on how many columns a CTA was given.  Rows are
 // staged in shared memory sixteen at a time (activations and the two exponentials applied once, on
-// the way in).  Outputs are float rows [T, heads * vdim]: the norm and gate that follow them are a
+// the way in) by four warps that hold no state, into the stage the others are not reading: the
+// warps that walk the rows never wait for global memory, and meet the others once per sixteen rows.  Outputs are float rows [T, heads * vdim]: the norm and gate that follow them are a
 // row kernel's.
 #include "common.cuh"
 
@@ -34,20 +35,20 @@ struct StateRecurrenceArgs {
 
 __device__ __forceinline__ float sr_silu(float z) { return z / (1.0f + expf(-z)); }
 
+#define SR_PRODUCERS 128  // threads behind the ones that hold state: they stage the next rows
+
 template <typename AT, int RPT>
-__global__ void __launch_bounds__(256) state_recurrence_kernel(const StateRecurrenceArgs a) {
+__global__ void __launch_bounds__(256 + SR_PRODUCERS) state_recurrence_kernel(const StateRecurrenceArgs a) {
     const int h = blockIdx.x, s = blockIdx.y, col0 = blockIdx.z * a.cols;
+    const int workers = a.cols * 4;  // threads that hold state; the rest stage rows
+    const bool producer = (int)threadIdx.x >= workers;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int part = lane & 3, local = warp * 8 + (lane >> 2), col = col0 + local;
-    const bool live = col < a.vdim;
+    const bool live = !producer && col < a.vdim;
     const int dim = a.dim, vdim = a.vdim, g = h / (a.heads / a.groups);
     constexpr int DP = 4 * RPT;             // key rows with padding (zeros: their state stays zero)
     extern __shared__ __align__(16) float sm[];
-    float* sq = sm;                         // [SR_TOKENS][DP]
-    float* sk = sq + SR_TOKENS * DP;        // [SR_TOKENS][DP]
-    float* sv = sk + SR_TOKENS * DP;        // [SR_TOKENS][cols]
-    float* sa = sv + SR_TOKENS * a.cols;    // [SR_TOKENS]
-    float* sb = sa + SR_TOKENS;             // [SR_TOKENS]
+    const int stage_floats = 2 * SR_TOKENS * DP + SR_TOKENS * a.cols + 2 * SR_TOKENS;  // q, k, v, decay, input scale
     const float skip = a.skip ? a.skip[h] : 0.0f;
     const float loss = a.head_loss ? a.head_loss[h] : 0.0f;
     const float rate = a.a_log ? expf(a.a_log[h]) : 0.0f;
@@ -67,70 +68,108 @@ __global__ void __launch_bounds__(256) state_recurrence_kernel(const StateRecurr
     const AT* vp = (const AT*)a.v + (size_t)h * vdim + col0;
     const AT* dtp = a.dt ? (const AT*)a.dt + h : nullptr;
     float* op = a.out + (size_t)h * vdim + col;
-    for (int base = 0; base < n; base += SR_TOKENS) {
+
+    // Rows base .. base + count - 1 into a stage, by `threads` threads of which this is number `me`.
+    // Eight loads are asked for before the first is converted, at addresses that are valid whatever
+    // the count (a place beyond it reads the chunk's first row and stores zero).
+    auto stage_rows = [&](int base, float* st, int me, int threads) {
         const int count = min(SR_TOKENS, n - base);
         const size_t row0 = (size_t)(first + base);
-        for (int i = threadIdx.x; i < count * DP; i += blockDim.x) {
-            const int t = i / DP, c = i - t * DP;
-            float qv = 0.0f, kv = 0.0f;
-            if (c < dim) {
-                qv = to_f32(qp[(row0 + t) * a.q_ld + c]), kv = to_f32(kp[(row0 + t) * a.k_ld + c]);
-                if (a.silu) qv = sr_silu(qv), kv = sr_silu(kv);
+        float* sq = st;
+        float* sk = sq + SR_TOKENS * DP;
+        float* sv = sk + SR_TOKENS * DP;
+        float* sa = sv + SR_TOKENS * a.cols;
+        float* sb = sa + SR_TOKENS;
+        for (int i0 = me; i0 < SR_TOKENS * DP; i0 += threads * 4) {
+            float qv[4], kv[4];
+            bool ok[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * threads, t = i / DP, c = i - t * DP;
+                ok[u] = i < SR_TOKENS * DP && t < count && c < dim;
+                const size_t at_t = ok[u] ? row0 + t : row0;
+                const int at_c = ok[u] ? c : 0;
+                qv[u] = to_f32(qp[at_t * a.q_ld + at_c]);
+                kv[u] = to_f32(kp[at_t * a.k_ld + at_c]);
             }
-            sq[i] = qv;
-            sk[i] = kv;
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * threads;
+                if (i >= SR_TOKENS * DP) continue;
+                if (a.silu) qv[u] = sr_silu(qv[u]), kv[u] = sr_silu(kv[u]);
+                sq[i] = ok[u] ? qv[u] : 0.0f;
+                sk[i] = ok[u] ? kv[u] : 0.0f;
+            }
         }
-        for (int i = threadIdx.x; i < count * a.cols; i += blockDim.x) {
+        for (int i = me; i < count * a.cols; i += threads) {
             const int t = i / a.cols, c = i - t * a.cols;
             float vv = (col0 + c < vdim) ? to_f32(vp[(row0 + t) * a.v_ld + c]) : 0.0f;
             if (a.silu) vv = sr_silu(vv);
             sv[t * a.cols + c] = vv;
         }
         if (dtp) {
-            for (int t = threadIdx.x; t < count; t += blockDim.x) {
+            for (int t = me; t < count; t += threads) {
                 const float z = to_f32(dtp[(row0 + t) * a.dt_ld]) + dt_bias;
                 const float step = z > 20.0f ? z : log1pf(expf(z));
                 sb[t] = step;
                 sa[t] = expf(-rate * step);
             }
         }
-        __syncthreads();
-        for (int t = 0; t < count; ++t) {
-            const float4* qt = reinterpret_cast<const float4*>(sq + t * DP) + part;
-            const float4* kt = reinterpret_cast<const float4*>(sk + t * DP) + part;
-            const float vt = sv[t * a.cols + local];
-            float acc = 0.0f;
-            if (dtp) {
-                const float decay = sa[t], bv = sb[t] * vt;
+    };
+
+    stage_rows(0, sm, threadIdx.x, blockDim.x);  // the first rows: everybody
+    __syncthreads();
+    int buf = 0;
+    for (int base = 0; base < n; base += SR_TOKENS, buf ^= 1) {
+        const int count = min(SR_TOKENS, n - base);
+        if (producer) {
+            if (base + SR_TOKENS < n) stage_rows(base + SR_TOKENS, sm + (buf ^ 1) * stage_floats, threadIdx.x - workers, blockDim.x - workers);
+        } else {
+            const float* st = sm + buf * stage_floats;
+            const float* sq = st;
+            const float* sk = sq + SR_TOKENS * DP;
+            const float* sv = sk + SR_TOKENS * DP;
+            const float* sa = sv + SR_TOKENS * a.cols;
+            const float* sb = sa + SR_TOKENS;
+            const size_t row0 = (size_t)(first + base);
+            for (int t = 0; t < count; ++t) {
+                const float4* qt = reinterpret_cast<const float4*>(sq + t * DP) + part;
+                const float4* kt = reinterpret_cast<const float4*>(sk + t * DP) + part;
+                const float vt = sv[t * a.cols + local];
+                float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;  // four chains instead of one of dim / 4 links
+                if (dtp) {
+                    const float decay = sa[t], bv = sb[t] * vt;
 #pragma unroll
-                for (int j = 0; j < RPT / 4; ++j) {
-                    const float4 k4 = kt[4 * j], q4 = qt[4 * j];
-                    S[4 * j] = fmaf(decay, S[4 * j], k4.x * bv);
-                    S[4 * j + 1] = fmaf(decay, S[4 * j + 1], k4.y * bv);
-                    S[4 * j + 2] = fmaf(decay, S[4 * j + 2], k4.z * bv);
-                    S[4 * j + 3] = fmaf(decay, S[4 * j + 3], k4.w * bv);
-                    acc = fmaf(S[4 * j], q4.x, acc);
-                    acc = fmaf(S[4 * j + 1], q4.y, acc);
-                    acc = fmaf(S[4 * j + 2], q4.z, acc);
-                    acc = fmaf(S[4 * j + 3], q4.w, acc);
-                }
-            } else {
+                    for (int j = 0; j < RPT / 4; ++j) {
+                        const float4 k4 = kt[4 * j], q4 = qt[4 * j];
+                        S[4 * j] = fmaf(decay, S[4 * j], k4.x * bv);
+                        S[4 * j + 1] = fmaf(decay, S[4 * j + 1], k4.y * bv);
+                        S[4 * j + 2] = fmaf(decay, S[4 * j + 2], k4.z * bv);
+                        S[4 * j + 3] = fmaf(decay, S[4 * j + 3], k4.w * bv);
+                        a0 = fmaf(S[4 * j], q4.x, a0);
+                        a1 = fmaf(S[4 * j + 1], q4.y, a1);
+                        a2 = fmaf(S[4 * j + 2], q4.z, a2);
+                        a3 = fmaf(S[4 * j + 3], q4.w, a3);
+                    }
+                } else {
 #pragma unroll
-                for (int j = 0; j < RPT / 4; ++j) {
-                    const float4 k4 = kt[4 * j], q4 = qt[4 * j];
-                    S[4 * j] = fmaf(k4.x, vt, fmaf(-loss, S[4 * j], S[4 * j]));
-                    S[4 * j + 1] = fmaf(k4.y, vt, fmaf(-loss, S[4 * j + 1], S[4 * j + 1]));
-                    S[4 * j + 2] = fmaf(k4.z, vt, fmaf(-loss, S[4 * j + 2], S[4 * j + 2]));
-                    S[4 * j + 3] = fmaf(k4.w, vt, fmaf(-loss, S[4 * j + 3], S[4 * j + 3]));
-                    acc = fmaf(S[4 * j], q4.x, acc);
-                    acc = fmaf(S[4 * j + 1], q4.y, acc);
-                    acc = fmaf(S[4 * j + 2], q4.z, acc);
-                    acc = fmaf(S[4 * j + 3], q4.w, acc);
+                    for (int j = 0; j < RPT / 4; ++j) {
+                        const float4 k4 = kt[4 * j], q4 = qt[4 * j];
+                        S[4 * j] = fmaf(k4.x, vt, fmaf(-loss, S[4 * j], S[4 * j]));
+                        S[4 * j + 1] = fmaf(k4.y, vt, fmaf(-loss, S[4 * j + 1], S[4 * j + 1]));
+                        S[4 * j + 2] = fmaf(k4.z, vt, fmaf(-loss, S[4 * j + 2], S[4 * j + 2]));
+                        S[4 * j + 3] = fmaf(k4.w, vt, fmaf(-loss, S[4 * j + 3], S[4 * j + 3]));
+                        a0 = fmaf(S[4 * j], q4.x, a0);
+                        a1 = fmaf(S[4 * j + 1], q4.y, a1);
+                        a2 = fmaf(S[4 * j + 2], q4.z, a2);
+                        a3 = fmaf(S[4 * j + 3], q4.w, a3);
+                    }
                 }
+                float acc = (a0 + a1) + (a2 + a3);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+                acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+                if (live && part == 0) op[(row0 + t) * ((size_t)a.heads * vdim)] = fmaf(skip, vt, acc);
             }
-            acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-            acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            if (live && part == 0) op[(row0 + t) * ((size_t)a.heads * vdim)] = fmaf(skip, vt, acc);
         }
         __syncthreads();
     }
@@ -151,11 +190,11 @@ static int launch_state_recurrence(const StateRecurrenceArgs& a, int num_seqs, i
     while (cols > 8 && cols / 2 >= a.vdim) cols /= 2;
     StateRecurrenceArgs args = a;
     args.cols = cols;
-    const dim3 grid(a.heads, num_seqs, (a.vdim + cols - 1) / cols), block(cols * 4);
+    const dim3 grid(a.heads, num_seqs, (a.vdim + cols - 1) / cols), block(cols * 4 + SR_PRODUCERS);
     const int rpt = (a.dim + 15) / 16 * 4;  // key rows in runs of 16: four to each of a column's four lanes
 #define SR_CASE(R)                                                                                                   \
     if (rpt <= R) {                                                                                                  \
-        const size_t smem = (size_t)(2 * SR_TOKENS * 4 * R + SR_TOKENS * cols + 2 * SR_TOKENS) * sizeof(float);      \
+        const size_t smem = (size_t)2 * (2 * SR_TOKENS * 4 * R + SR_TOKENS * cols + 2 * SR_TOKENS) * sizeof(float);  \
         auto kern = state_recurrence_kernel<AT, R>;                                                                  \
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
         launch_kernel(kern, grid, block, smem, stream, args);                                                        \
