@@ -79,6 +79,8 @@ _SIGNATURES = {
     "shiso_routed_experts": [P, I, P, P, P, P, I, P, P, P, P, P, I, I, I, I, I, P],
     "shiso_latent_attention_smem": [I, I],
     "shiso_latent_attention": [P, I, P, P, I, P, P, P, P, I, I, I, I, I, F, I, P],
+    "shiso_latent_prefill_supported": [I, I],
+    "shiso_latent_prefill": [P, P, P, I, P, P, P, I, I, I, I, I, I, F, P],
 }
 
 

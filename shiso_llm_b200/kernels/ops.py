@@ -1329,10 +1329,15 @@ LATENT_DECODE_SHARE_KEYS = 1024  # a decode step's keys are shared out over CTAs
 LATENT_MAX_SHARES = 16  # ... up to this many CTAs a (row, head group)
 
 
-def latent_attention(q_lat, rank, k_cache, block_table, page_size, scale, step):
+LATENT_MMA_MIN_PORTION = 8  # steps whose longest portion has at least this many rows take the tensor-core kernel (bfloat16)
+
+
+def latent_attention(q_lat, rank, k_cache, block_table, page_size, scale, step, general=False):
     """Causal softmax attention of ``q_lat[T, H, W]`` against the cached rows ``k_cache[pages, page_size,
     1, W]`` of each row's sequence; the values are the first ``rank`` entries of the same rows.
-    Returns ``[T, H, rank]`` in the input type."""
+    Returns ``[T, H, rank]`` in the input type.  bfloat16 steps with prompt portions take the
+    tensor-core kernel (16 rows of a sequence and eight heads a CTA) where the widths allow it;
+    steps of single tokens, float32 and other widths the general kernel, which ``general=True`` forces."""
     _check(q_lat, "q", None, 3)
     tokens, heads, width = q_lat.shape
     _paged(k_cache, "latent cache", q_lat.dtype, page_size)
@@ -1340,6 +1345,22 @@ def latent_attention(q_lat, rank, k_cache, block_table, page_size, scale, step):
         raise KernelError(f"a cache of shape {tuple(k_cache.shape)} for queries of {width} and a latent of {rank}")
     _check(block_table, "block table", torch.int32, 2)
     out = torch.empty((tokens, heads, rank), dtype=q_lat.dtype, device=q_lat.device)
+    lib = library()
+    if (
+        not general and q_lat.dtype == torch.bfloat16 and not getattr(step, "all_decode", False)
+        and getattr(step, "max_q_len", tokens) >= LATENT_MMA_MIN_PORTION and lib.shiso_latent_prefill_supported(int(rank), width)
+    ):
+        starts = getattr(step, "h_q_start", None)
+        if starts:
+            tiles = sum(-(-(b - a) // 16) for a, b in zip(starts[:-1], starts[1:]))
+        else:
+            tiles = tokens // 16 + step.num_seqs
+        status = lib.shiso_latent_prefill(
+            _ptr(q_lat), _ptr(k_cache), _ptr(block_table), block_table.shape[1], _ptr(step.q_start), _ptr(step.start_pos), _ptr(out),
+            step.num_seqs, tiles, heads, int(rank), width, page_size, float(scale), _stream(),
+        )
+        _done(status, "latent_attention (mma, prompt portions)", shape=(tokens, heads, width))
+        return out
     # steps of single tokens at long contexts: a row's keys go to several CTAs (the split depends on the step's shape only)
     shares, scratch = 1, None
     if getattr(step, "all_decode", False):
