@@ -1325,7 +1325,7 @@ def head_linear(x, w, out, gate=None):
     return out
 
 
-LATENT_DECODE_SHARE_KEYS = 1024  # a decode step's keys are shared out over CTAs in ranges of about this many ...
+LATENT_DECODE_SHARE_KEYS = 256  # a decode step's keys are shared out over CTAs in ranges of about this many (a run of 32 per warp) ...
 LATENT_MAX_SHARES = 16  # ... up to this many CTAs a (row, head group)
 
 
@@ -1365,7 +1365,7 @@ def latent_attention(q_lat, rank, k_cache, block_table, page_size, scale, step, 
     shares, scratch = 1, None
     if getattr(step, "all_decode", False):
         context = block_table.shape[1] * page_size
-        shares = max(1, min(LATENT_MAX_SHARES, context // LATENT_DECODE_SHARE_KEYS, _sm_count() // max(1, tokens * -(-heads // 4))))
+        shares = max(1, min(LATENT_MAX_SHARES, context // LATENT_DECODE_SHARE_KEYS, 2 * _sm_count() // max(1, tokens * -(-heads // 4))))  # two CTAs fit an SM
         if shares > 1:
             scratch = torch.empty((tokens * heads * shares * (rank + 2),), dtype=torch.float32, device=q_lat.device)
     status = library().shiso_latent_attention(
