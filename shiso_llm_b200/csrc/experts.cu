@@ -132,16 +132,17 @@ __global__ void __launch_bounds__(256) tile_gemm_kernel(const TileGemmArgs a) {
 }
 
 // ---- the same products on the tensor cores (bfloat16 inputs) -------------------------------
-// 64 rows x 128 outputs per CTA and 32 columns of K per stage, eight warps of 32 x 32 outputs,
+// 64 rows x 128 outputs per CTA and 64 columns of K per stage, eight warps of 32 x 32 outputs,
 // mma.sync m16n8k16 with float accumulators; rows (gathered through the same index) and matrix rows
 // come by 16-byte cp.async into three stages of padded shared-memory rows that ldmatrix reads without
 // bank conflicts.  With a stacked gate/up matrix both halves are accumulated and the epilogue
 // writes silu(gate) * up.  Needs K, the row strides and the batch strides to be multiples of 8.
 #define TM_BM 64
 #define TM_BN 128
-#define TM_BK 32
-#define TM_ROW 80  // bytes of a padded shared-memory row: 32 bfloat16 + 16 bytes
+#define TM_BK 64
+#define TM_ROW (TM_BK * 2 + 16)  // bytes of a padded shared-memory row: TM_BK bfloat16 + 16 bytes
 #define TM_STAGES 3
+#define TM_PIECES (TM_BK / 8)  // 16-byte pieces of a row
 
 __device__ __forceinline__ uint32_t tm_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void tm_cp16(void* dst, const void* src, bool valid) {
@@ -190,20 +191,29 @@ __global__ void __launch_bounds__(256) tile_gemm_mma_kernel(const TileGemmArgs a
     const int n0 = blockIdx.x * TM_BN;
     const __nv_bfloat16* x = (const __nv_bfloat16*)a.x + (size_t)batch * a.x_bs;
     const __nv_bfloat16* w = (const __nv_bfloat16*)a.w + (size_t)batch * a.w_bs;
-    // this thread's copies: one 16-byte piece of an input row, WROWS / 64 pieces of matrix rows
-    const int xr = tid >> 2, piece = tid & 3;
-    const __nv_bfloat16* xsrc = nullptr;
-    if (row0 + xr < row_end) {
-        const int m = row0 + xr;
-        xsrc = x + (size_t)(a.gather ? a.gather[m] / a.gather_div : m) * a.x_ld;
+    // this thread's copies per stage: TM_BM * TM_PIECES / 256 pieces of input rows, WROWS * TM_PIECES / 256 of matrix rows
+    constexpr int XCOPIES = TM_BM * TM_PIECES / 256, WCOPIES = WROWS * TM_PIECES / 256;
+    const __nv_bfloat16* xsrc[XCOPIES];
+#pragma unroll
+    for (int i = 0; i < XCOPIES; ++i) {
+        const int r = (tid + i * 256) / TM_PIECES;
+        xsrc[i] = nullptr;
+        if (row0 + r < row_end) {
+            const int m = row0 + r;
+            xsrc[i] = x + (size_t)(a.gather ? a.gather[m] / a.gather_div : m) * a.x_ld;
+        }
     }
     auto load = [&](int k0, int stage) {
-        const int k = k0 + piece * 8;
-        tm_cp16(xs + (stage * TM_BM + xr) * TM_ROW + piece * 16, xsrc ? xsrc + k : x, xsrc != nullptr && k < a.K);
 #pragma unroll
-        for (int i = 0; i < WROWS / 64; ++i) {
-            const int r = xr + 64 * i;               // row of the stage: gate rows, then up rows
-            const int half = r / TM_BN, n = n0 + r % TM_BN;
+        for (int i = 0; i < XCOPIES; ++i) {
+            const int idx = tid + i * 256, r = idx / TM_PIECES, piece = idx % TM_PIECES, k = k0 + piece * 8;
+            const bool ok = xsrc[i] != nullptr && k < a.K;
+            tm_cp16(xs + (stage * TM_BM + r) * TM_ROW + piece * 16, ok ? xsrc[i] + k : x, ok);
+        }
+#pragma unroll
+        for (int i = 0; i < WCOPIES; ++i) {
+            const int idx = tid + i * 256, r = idx / TM_PIECES, piece = idx % TM_PIECES, k = k0 + piece * 8;
+            const int half = r / TM_BN, n = n0 + r % TM_BN;  // rows of the stage: gate rows, then up rows
             const bool ok = n < a.N && k < a.K;
             tm_cp16(ws + (stage * WROWS + r) * TM_ROW + piece * 16, ok ? w + ((size_t)half * a.N + n) * a.K + k : w, ok);
         }
@@ -212,15 +222,18 @@ __global__ void __launch_bounds__(256) tile_gemm_mma_kernel(const TileGemmArgs a
     const int wm = warp >> 2, wn = warp & 3;
     float acc[2][4][4] = {}, acc2[GLU ? 2 : 1][4][4] = {};
     const int steps = (a.K + TM_BK - 1) / TM_BK;
+    // stages s and s + 1 are on their way while stage s is worked on; one barrier a step: when a
+    // thread passes it, stage s has landed for everybody and nobody still reads stage s - 1,
+    // which is the one the next copies fill
     load(0, 0);
     if (steps > 1) load(TM_BK, 1);
     else asm volatile("cp.async.commit_group;" ::: "memory");
     for (int s = 0; s < steps; ++s) {
         const int stage = s % TM_STAGES;
-        if (s + 2 < steps) load((s + 2) * TM_BK, (s + 2) % TM_STAGES);  // the stage that was read an iteration ago
-        else asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 2;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");
         __syncthreads();
+        if (s + 2 < steps) load((s + 2) * TM_BK, (s + 2) % TM_STAGES);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
         const uint8_t* xt = xs + stage * TM_BM * TM_ROW;
         const uint8_t* wt = ws + stage * WROWS * TM_ROW;
 #pragma unroll
@@ -253,7 +266,6 @@ __global__ void __launch_bounds__(256) tile_gemm_mma_kernel(const TileGemmArgs a
                 }
             }
         }
-        __syncthreads();
     }
     pdl_trigger();
     OT* out = (OT*)a.out + (size_t)batch * a.out_bs;

@@ -70,7 +70,7 @@ __global__ void __launch_bounds__(256 + SR_PRODUCERS) state_recurrence_kernel(co
     float* op = a.out + (size_t)h * vdim + col;
 
     // Rows base .. base + count - 1 into a stage, by `threads` threads of which this is number `me`.
-    // Eight loads are asked for before the first is converted, at addresses that are valid whatever
+    // Sixteen loads are asked for before the first is converted, at addresses that are valid whatever
     // the count (a place beyond it reads the chunk's first row and stores zero).
     auto stage_rows = [&](int base, float* st, int me, int threads) {
         const int count = min(SR_TOKENS, n - base);
@@ -80,11 +80,12 @@ __global__ void __launch_bounds__(256 + SR_PRODUCERS) state_recurrence_kernel(co
         float* sv = sk + SR_TOKENS * DP;
         float* sa = sv + SR_TOKENS * a.cols;
         float* sb = sa + SR_TOKENS;
-        for (int i0 = me; i0 < SR_TOKENS * DP; i0 += threads * 4) {
-            float qv[4], kv[4];
-            bool ok[4];
+        constexpr int U = 8;  // loads of q and of k a thread has in flight
+        for (int i0 = me; i0 < SR_TOKENS * DP; i0 += threads * U) {
+            float qv[U], kv[U];
+            bool ok[U];
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < U; ++u) {
                 const int i = i0 + u * threads, t = i / DP, c = i - t * DP;
                 ok[u] = i < SR_TOKENS * DP && t < count && c < dim;
                 const size_t at_t = ok[u] ? row0 + t : row0;
@@ -93,7 +94,7 @@ __global__ void __launch_bounds__(256 + SR_PRODUCERS) state_recurrence_kernel(co
                 kv[u] = to_f32(kp[at_t * a.k_ld + at_c]);
             }
 #pragma unroll
-            for (int u = 0; u < 4; ++u) {
+            for (int u = 0; u < U; ++u) {
                 const int i = i0 + u * threads;
                 if (i >= SR_TOKENS * DP) continue;
                 if (a.silu) qv[u] = sr_silu(qv[u]), kv[u] = sr_silu(kv[u]);
@@ -101,11 +102,22 @@ __global__ void __launch_bounds__(256 + SR_PRODUCERS) state_recurrence_kernel(co
                 sk[i] = ok[u] ? kv[u] : 0.0f;
             }
         }
-        for (int i = me; i < count * a.cols; i += threads) {
-            const int t = i / a.cols, c = i - t * a.cols;
-            float vv = (col0 + c < vdim) ? to_f32(vp[(row0 + t) * a.v_ld + c]) : 0.0f;
-            if (a.silu) vv = sr_silu(vv);
-            sv[t * a.cols + c] = vv;
+        for (int i0 = me; i0 < SR_TOKENS * a.cols; i0 += threads * 4) {
+            float vv[4];
+            bool ok[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * threads, t = i / a.cols, c = i - t * a.cols;
+                ok[u] = i < SR_TOKENS * a.cols && t < count && col0 + c < vdim;
+                vv[u] = to_f32(vp[(ok[u] ? row0 + t : row0) * a.v_ld + (ok[u] ? c : 0)]);
+            }
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int i = i0 + u * threads;
+                if (i >= SR_TOKENS * a.cols) continue;
+                if (a.silu) vv[u] = sr_silu(vv[u]);
+                sv[i] = ok[u] ? vv[u] : 0.0f;
+            }
         }
         if (dtp) {
             for (int t = me; t < count; t += threads) {

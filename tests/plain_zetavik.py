@@ -162,10 +162,29 @@ def route(scores, top, group_count, group_keep):
     return chosen
 
 
-def moe_ff(tensors, prefix, mlp, h):
+def route_margin(scores, chosen, group_count):
+    """Per row: how far the choice was from falling otherwise, as a share of the score at stake -
+    the smaller of (worst chosen score - best score left out) and (worst kept group - best dropped
+    group); ``inf`` where nothing was left out."""
+    T, E = scores.shape
+    inf = torch.full((T,), float("inf"), dtype=F64)
+    low = torch.where(chosen, scores, torch.full_like(scores, float("inf"))).min(-1).values
+    out = torch.where(~chosen, scores, torch.full_like(scores, -1.0)).max(-1).values
+    margin = torch.where(out >= 0, (low - out).abs() / low.clamp_min(1e-30), inf)
+    groups = scores.reshape(T, group_count, E // group_count)
+    best = groups.max(-1).values
+    kept = chosen.reshape(T, group_count, E // group_count).any(-1)
+    low_g = torch.where(kept, best, torch.full_like(best, float("inf"))).min(-1).values
+    out_g = torch.where(~kept, best, torch.full_like(best, -1.0)).max(-1).values
+    return torch.minimum(margin, torch.where(out_g >= 0, (low_g - out_g).abs() / low_g.clamp_min(1e-30), inf))
+
+
+def moe_ff(tensors, prefix, mlp, h, margins=None):
     r = mlp["router"]
     scores = torch.softmax(h @ _w(tensors, f"{prefix}.router").T, dim=-1)
     chosen = route(scores, r["top"], r["groups"]["count"], r["groups"]["keep"])
+    if margins is not None:
+        margins.append(route_margin(scores, chosen, r["groups"]["count"]))
     weights = scores * chosen * r["scale"]
     out = torch.zeros_like(h)
     for e in range(r["experts"]):
@@ -182,9 +201,9 @@ def moe_ff(tensors, prefix, mlp, h):
 MIXERS = {"mamba2": mamba2, "latent_attention": latent_attention, "lightning": lightning}
 
 
-def forward(doc, tensors, tokens, after_layer=None):
+def forward(doc, tensors, tokens, after_layer=None, margins=None):
     """Logits ``[T, vocab]`` (float64) of a whole sequence; ``after_layer(i, x)`` sees the
-    residual rows after every layer."""
+    residual rows after every layer; a list ``margins`` is given one ``route_margin`` per routed layer."""
     eps = doc["norm"]["eps"]
     table = _w(tensors, "embed")
     x = table[torch.as_tensor(tokens, dtype=torch.long)]
@@ -193,7 +212,7 @@ def forward(doc, tensors, tokens, after_layer=None):
         y = MIXERS[layer["type"]](tensors, f"l{i}.mix", layer["mixer"], h, eps)
         mlp = layer.get("mlp")
         if mlp is not None:
-            y = y + (dense_ff(tensors, f"l{i}.mlp", h) if mlp["kind"] == "dense" else moe_ff(tensors, f"l{i}.mlp", mlp, h))
+            y = y + (dense_ff(tensors, f"l{i}.mlp", h) if mlp["kind"] == "dense" else moe_ff(tensors, f"l{i}.mlp", mlp, h, margins))
         x = x + y
         if after_layer is not None:
             after_layer(i, x)

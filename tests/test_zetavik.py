@@ -86,30 +86,44 @@ DOC_C = {
 DOCS = {"A": (DOC_A, 3), "B": (DOC_B, 4), "C": (DOC_C, 5)}
 
 
+CLOSE_CALL = 0.05  # a choice of the router that a tenth of the score at stake would have turned
+
+
 def check_rows(got, ref, dtype, what):
     """Per-row error against the plain logits, relative to their spread.  float32: sums in another
     order, rsqrtf/expf/sincosf and recurrences carried in float32 stay below 1e-4 of the spread;
     bfloat16: matrices, activations and the cache rounded to 8 bits of mantissa through a few
-    layers stay below a tenth.  A wrong key, state, page or expert moves a row by the spread itself."""
+    layers stay below a tenth.  A wrong key, state, page or expert moves a row by the spread itself.
+    ``ref`` may carry ``margin`` (per row, the router's closest call over all layers): in bfloat16 a
+    row whose choice of experts hung on less than CLOSE_CALL of a score may choose otherwise, and is
+    held to finiteness and half the spread only - no test rests on a close call."""
+    margin = getattr(ref, "margin", None)
     got, ref = got.double(), ref.double()
     assert got.shape == ref.shape, (what, got.shape, ref.shape)
     assert torch.isfinite(got).all(), f"{what}: non-finite logits"
     spread = ref.std().item()
     rms = (got - ref).pow(2).mean(-1).sqrt() / spread
     bound = 1e-4 if dtype == "float32" else 0.1
+    if dtype != "float32" and margin is not None:
+        close_call = margin < CLOSE_CALL
+        assert rms[close_call].numel() == 0 or rms[close_call].max().item() <= 0.5, f"{what}: a row with a close call is off by more than half the spread"
+        # a row after a close call carries a trace of it (its state and keys hold the other expert's output): twice the bound
+        after = torch.cumsum(close_call.long(), 0) > 0
+        rms = torch.where(close_call, torch.zeros_like(rms), torch.where(after, rms / 2, rms))
     worst = int(rms.argmax())
-    if dtype != "float32":
-        # a router's choice between two experts whose scores differ by less than bfloat16 resolves may
-        # fall the other way: a row in a hundred may move by more, by far less than a wrong key would
-        over = int((rms > bound).sum())
-        assert over <= max(1, rms.numel() // 100) and rms.max().item() <= 0.3, \
-            f"{what}: {over} rows over {bound}, row {worst} differs by {rms.max().item():.3e} of the spread"
-        return
     assert rms.max().item() <= bound, f"{what}: row {worst} differs by {rms.max().item():.3e} of the spread (> {bound})"
 
 
+class Reference(torch.Tensor):
+    """Plain logits that remember the router's closest call of every row."""
+
+
 def reference_logits(doc, tensors, tokens):
-    return plain.forward(doc, dict(tensors), tokens)
+    margins = []
+    logits = plain.forward(doc, dict(tensors), tokens, margins=margins)
+    out = logits.as_subclass(Reference)
+    out.margin = torch.stack(margins).min(0).values if margins else None
+    return out
 
 
 # --------------------------------------------------------------------------- configuration

@@ -95,7 +95,7 @@ def test_latent_store_and_rotation(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("shape", [(70, 5, 24, 40), (3, 2, 7, 9), (200, 16, 224, 64), (130, 8, 64, 224)])
+@pytest.mark.parametrize("shape", [(70, 5, 24, 40), (3, 2, 7, 9), (200, 16, 224, 64), (130, 8, 64, 224), (70, 2, 130, 456)])
 def test_products_per_head(dtype, shape):
     tokens, heads, n, k = shape
     t = ops()
@@ -111,7 +111,7 @@ def test_products_per_head(dtype, shape):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("shape", [(90, 40, 24, 6, 2), (5, 36, 10, 5, 5), (300, 128, 96, 8, 3), (1, 64, 32, 16, 4)])
+@pytest.mark.parametrize("shape", [(90, 40, 24, 6, 2), (5, 36, 10, 5, 5), (300, 128, 96, 8, 3), (1, 64, 32, 16, 4), (200, 520, 264, 4, 2)])
 def test_routing_and_experts(dtype, shape):
     tokens, hidden, ff, experts, top = shape
     t = ops()
