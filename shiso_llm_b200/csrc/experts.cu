@@ -132,16 +132,16 @@ __global__ void __launch_bounds__(256) tile_gemm_kernel(const TileGemmArgs a) {
 }
 
 // ---- the same products on the tensor cores (bfloat16 inputs) -------------------------------
-// 64 rows x 128 outputs per CTA and 64 columns of K per stage, eight warps of 32 x 32 outputs,
+// 64 rows x 128 outputs per CTA and 32 columns of K per stage, eight warps of 32 x 32 outputs,
 // mma.sync m16n8k16 with float accumulators; rows (gathered through the same index) and matrix rows
-// come by 16-byte cp.async into three stages of padded shared-memory rows that ldmatrix reads without
+// come by 16-byte cp.async into four stages of padded shared-memory rows that ldmatrix reads without
 // bank conflicts.  With a stacked gate/up matrix both halves are accumulated and the epilogue
 // writes silu(gate) * up.  Needs K, the row strides and the batch strides to be multiples of 8.
 #define TM_BM 64
 #define TM_BN 128
-#define TM_BK 64
+#define TM_BK 32
 #define TM_ROW (TM_BK * 2 + 16)  // bytes of a padded shared-memory row: TM_BK bfloat16 + 16 bytes
-#define TM_STAGES 3
+#define TM_STAGES 4
 #define TM_PIECES (TM_BK / 8)  // 16-byte pieces of a row
 
 __device__ __forceinline__ uint32_t tm_smem(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -222,17 +222,19 @@ __global__ void __launch_bounds__(256) tile_gemm_mma_kernel(const TileGemmArgs a
     const int wm = warp >> 2, wn = warp & 3;
     float acc[2][4][4] = {}, acc2[GLU ? 2 : 1][4][4] = {};
     const int steps = (a.K + TM_BK - 1) / TM_BK;
-    // stages s and s + 1 are on their way while stage s is worked on; one barrier a step: when a
+    // the next stages are on their way while stage s is worked on; one barrier a step: when a
     // thread passes it, stage s has landed for everybody and nobody still reads stage s - 1,
     // which is the one the next copies fill
-    load(0, 0);
-    if (steps > 1) load(TM_BK, 1);
-    else asm volatile("cp.async.commit_group;" ::: "memory");
+#pragma unroll
+    for (int p = 0; p < TM_STAGES - 1; ++p) {
+        if (p < steps) load(p * TM_BK, p);
+        else asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     for (int s = 0; s < steps; ++s) {
         const int stage = s % TM_STAGES;
-        asm volatile("cp.async.wait_group 1;" ::: "memory");
+        asm volatile("cp.async.wait_group %0;" ::"n"(TM_STAGES - 2) : "memory");
         __syncthreads();
-        if (s + 2 < steps) load((s + 2) * TM_BK, (s + 2) % TM_STAGES);
+        if (s + TM_STAGES - 1 < steps) load((s + TM_STAGES - 1) * TM_BK, (s + TM_STAGES - 1) % TM_STAGES);
         else asm volatile("cp.async.commit_group;" ::: "memory");
         const uint8_t* xt = xs + stage * TM_BM * TM_ROW;
         const uint8_t* wt = ws + stage * WROWS * TM_ROW;
