@@ -22,7 +22,7 @@ reference's own benchmark scenarios (350M shape: 64 concurrent requests; 2.6B sh
 beside 32 decoding streams), unless ``--points`` leaves them out.
 
 ``--designs PRESET[,PRESET...]`` leaves the headline aside and prints, for each named preset
-(say ``filulix-1b,lfm2-1.2b``: two designs at one width, depth and feed-forward size), the time
+(say ``zetavik-1b,lfm2-1.2b,filulix-1b``: designs at one width, depth and active feed-forward size), the time
 of one prompt step and of a decode step at ``--batch`` and ``--prompt-len``, each with the
 table of its launches - the figures that set one design's kernels beside the other's.
 """

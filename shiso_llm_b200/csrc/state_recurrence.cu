@@ -31,9 +31,14 @@ struct StateRecurrenceArgs {
     const int *q_start, *state_slots;
     float* out;
     int heads, groups, dim, vdim, cols, silu;
+    int bulk;  // rows may be fetched 16 bytes at a time (widths, strides and addresses allow it)
 };
 
 __device__ __forceinline__ float sr_silu(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ void sr_cp16(void* dst, const void* src, bool valid) {
+    const int bytes = valid ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes) : "memory");
+}
 
 #define SR_PRODUCERS 128  // threads behind the ones that hold state: they stage the next rows
 
@@ -129,13 +134,71 @@ __global__ void __launch_bounds__(256 + SR_PRODUCERS) state_recurrence_kernel(co
         }
     };
 
+    // The same by the staging warps alone, with every byte of the sixteen rows in flight at once:
+    // 16-byte cp.async into a raw area of their own, one wait, a barrier among themselves, then the
+    // conversion (and activation) into the stage.  A row costs one trip to memory instead of several.
+    AT* raw = reinterpret_cast<AT*>(sm + 2 * stage_floats);  // [SR_TOKENS][dim] q, the same of k, [SR_TOKENS][cols] v
+    auto stage_rows_bulk = [&](int base, float* st, int me, int threads) {
+        constexpr int EPV = 16 / (int)sizeof(AT);  // elements a copy
+        const int count = min(SR_TOKENS, n - base);
+        const size_t row0 = (size_t)(first + base);
+        float* sq = st;
+        float* sk = sq + SR_TOKENS * DP;
+        float* sv = sk + SR_TOKENS * DP;
+        float* sa = sv + SR_TOKENS * a.cols;
+        float* sb = sa + SR_TOKENS;
+        AT* rq = raw;
+        AT* rk = rq + SR_TOKENS * dim;
+        AT* rv = rk + SR_TOKENS * dim;
+        const int qpieces = dim / EPV, vpieces = a.cols / EPV;
+        for (int i = me; i < SR_TOKENS * qpieces; i += threads) {
+            const int t = i / qpieces, c = (i - t * qpieces) * EPV;
+            const bool ok = t < count;
+            sr_cp16(rq + t * dim + c, ok ? qp + (row0 + t) * a.q_ld + c : qp, ok);
+            sr_cp16(rk + t * dim + c, ok ? kp + (row0 + t) * a.k_ld + c : kp, ok);
+        }
+        for (int i = me; i < SR_TOKENS * vpieces; i += threads) {
+            const int t = i / vpieces, c = (i - t * vpieces) * EPV;
+            const bool ok = t < count && col0 + c < vdim;
+            sr_cp16(rv + t * a.cols + c, ok ? vp + (row0 + t) * a.v_ld + c : vp, ok);
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        float z = 0.0f;
+        if (dtp && me < count) z = to_f32(dtp[(row0 + me) * a.dt_ld]) + dt_bias;
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");  // the staging warps among themselves
+        for (int i = me; i < SR_TOKENS * DP; i += threads) {
+            const int t = i / DP, c = i - t * DP;
+            float qv = 0.0f, kv = 0.0f;
+            if (c < dim && t < count) {
+                qv = to_f32(rq[t * dim + c]), kv = to_f32(rk[t * dim + c]);
+                if (a.silu) qv = sr_silu(qv), kv = sr_silu(kv);
+            }
+            sq[i] = qv;
+            sk[i] = kv;
+        }
+        for (int i = me; i < SR_TOKENS * a.cols; i += threads) {
+            float vv = to_f32(rv[i]);  // zeros where the copy was left out
+            if (a.silu) vv = sr_silu(vv);
+            sv[i] = vv;
+        }
+        if (dtp && me < count) {
+            const float step = z > 20.0f ? z : log1pf(expf(z));
+            sb[me] = step;
+            sa[me] = expf(-rate * step);
+        }
+    };  // (the block's barrier at the end of the sixteen rows also frees the raw area for the next ones)
+
     stage_rows(0, sm, threadIdx.x, blockDim.x);  // the first rows: everybody
     __syncthreads();
     int buf = 0;
     for (int base = 0; base < n; base += SR_TOKENS, buf ^= 1) {
         const int count = min(SR_TOKENS, n - base);
         if (producer) {
-            if (base + SR_TOKENS < n) stage_rows(base + SR_TOKENS, sm + (buf ^ 1) * stage_floats, threadIdx.x - workers, blockDim.x - workers);
+            if (base + SR_TOKENS < n) {
+                if (a.bulk) stage_rows_bulk(base + SR_TOKENS, sm + (buf ^ 1) * stage_floats, threadIdx.x - workers, blockDim.x - workers);
+                else stage_rows(base + SR_TOKENS, sm + (buf ^ 1) * stage_floats, threadIdx.x - workers, blockDim.x - workers);
+            }
         } else {
             const float* st = sm + buf * stage_floats;
             const float* sq = st;
@@ -202,11 +265,15 @@ static int launch_state_recurrence(const StateRecurrenceArgs& a, int num_seqs, i
     while (cols > 8 && cols / 2 >= a.vdim) cols /= 2;
     StateRecurrenceArgs args = a;
     args.cols = cols;
+    const int epv = 16 / (int)sizeof(AT);
+    args.bulk = a.dim % epv == 0 && a.vdim % epv == 0 && a.q_ld % epv == 0 && a.k_ld % epv == 0 && a.v_ld % epv == 0 &&
+                (((uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v) & 15) == 0;
     const dim3 grid(a.heads, num_seqs, (a.vdim + cols - 1) / cols), block(cols * 4 + SR_PRODUCERS);
     const int rpt = (a.dim + 15) / 16 * 4;  // key rows in runs of 16: four to each of a column's four lanes
 #define SR_CASE(R)                                                                                                   \
     if (rpt <= R) {                                                                                                  \
-        const size_t smem = (size_t)2 * (2 * SR_TOKENS * 4 * R + SR_TOKENS * cols + 2 * SR_TOKENS) * sizeof(float);  \
+        const size_t smem = (size_t)2 * (2 * SR_TOKENS * 4 * R + SR_TOKENS * cols + 2 * SR_TOKENS) * sizeof(float) + \
+                            (size_t)SR_TOKENS * (2 * a.dim + cols) * sizeof(AT);                                      \
         auto kern = state_recurrence_kernel<AT, R>;                                                                  \
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
         launch_kernel(kern, grid, block, smem, stream, args);                                                        \
@@ -227,7 +294,7 @@ SHISO_API int shiso_state_recurrence(const void* q, const void* k, const void* v
     if ((dt != nullptr) == (head_loss != nullptr)) return SHISO_ERR_UNSUPPORTED;  // one of the two forms
     if (dt && (!dt_bias || !a_log)) return SHISO_ERR_UNSUPPORTED;
     StateRecurrenceArgs a = {q, k, v, dt, q_ld, k_ld, v_ld, dt_ld, dt_bias, a_log, skip, head_loss, state, slot_stride,
-                             q_start, state_slots, out, heads, groups, dim, vdim, 0, silu};
+                             q_start, state_slots, out, heads, groups, dim, vdim, 0, silu, 0};
     if (act_dtype == SHISO_F32) return launch_state_recurrence<float>(a, num_seqs, sm_count, stream);
     if (act_dtype == SHISO_BF16) return launch_state_recurrence<__nv_bfloat16>(a, num_seqs, sm_count, stream);
     return SHISO_ERR_DTYPE;

@@ -29,6 +29,7 @@ from ..weights.spec import ONES, VECTOR, TensorSpec
 from .base import MIXERS, POSITION_ENCODINGS, DeferredLinear, Mixer, PagedKV, project
 
 MAX_LATENT_ROW = 1024  # kv_rank + rot_dim a CTA of the attention kernel keeps of a query in shared memory
+MAX_LATENT_RANK = 512  # kv_rank: a lane of the attention kernel sums up to 16 latent entries per head
 
 
 @MIXERS.register("latent_attention")
@@ -53,6 +54,8 @@ class LatentAttention(Mixer):
         self.eps = float(p["eps"])
         if self.kv_rank + self.rot > MAX_LATENT_ROW:
             raise UnsupportedShape("kv_rank + rot_dim", self.kv_rank + self.rot, f"the attention kernel takes cached rows of up to {MAX_LATENT_ROW}")
+        if self.kv_rank > MAX_LATENT_RANK:
+            raise UnsupportedShape("kv_rank", self.kv_rank, f"the attention kernel takes latents of up to {MAX_LATENT_RANK}")
         self.position = POSITION_ENCODINGS.build(p["position"], env, self.rot)
         if getattr(self.position, "interleaved", False):
             raise UnsupportedShape("position", p["position"].kind, "the kernels rotate half-split pairs")
