@@ -332,7 +332,8 @@ __global__ void __launch_bounds__(HG * 32) latent_prefill_mma_kernel(const Laten
             float s_acc[LP_BN / 8][4];
 #pragma unroll
             for (int j = 0; j < LP_BN / 8; ++j) s_acc[j][0] = s_acc[j][1] = s_acc[j][2] = s_acc[j][3] = 0.0f;
-            for (int kk = 0; kk < a.width / 16; ++kk) {
+#pragma unroll 4
+            for (int kk = 0; kk < a.width / 16; ++kk) {  // (unrolled so that the next fragments are asked for under this step's products)
                 uint32_t af[4];
                 {
                     const int r = warp * LP_BM + (lane & 7) + ((lane >> 3) & 1) * 8;

@@ -9,10 +9,11 @@
 // a group (head h reads group h / (heads / groups)); silu may be applied to q, k and v on load.
 //
 // One CTA walks the rows of one (head, sequence, range of value columns) in order.  A warp holds 8
-// columns; the key rows of a column are dealt to 4 lanes in runs of four (rows 16 j + 4 lane ..
-// + 3 to a lane, so that a lane reads its keys and queries as 16-byte words of shared memory); a
-// lane keeps dim / 4 state values in registers and an output is a sum over a lane's rows followed
-// by two shuffles: what is added to what, and in which order, depends on dim only - never on how
+// columns: a lane has two neighbouring columns and an eighth of the key rows, in runs of four (rows
+// 32 j + 4 lane .. + 3, so that a lane reads its keys and queries as 16-byte words of shared memory,
+// eight lanes a full 128-byte line, and uses each word for both of its columns); it keeps dim / 4
+// state values in registers and an output is a sum over a lane's rows followed by three shuffles:
+// what is added to what, and in which order, depends on dim only - never on how
 // the sequence was cut into steps, on the batch, or on how many columns a CTA was given.  Rows are
 // staged in shared memory sixteen at a time (activations and the two exponentials applied once, on
 // the way in) by four warps that hold no state, into the stage the others are not reading: the
@@ -48,10 +49,10 @@ __global__ void __launch_bounds__(256 + SR_PRODUCERS) state_recurrence_kernel(co
     const int workers = a.cols * 4;  // threads that hold state; the rest stage rows
     const bool producer = (int)threadIdx.x >= workers;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int part = lane & 3, local = warp * 8 + (lane >> 2), col = col0 + local;
-    const bool live = !producer && col < a.vdim;
+    const int part = lane & 7, local = warp * 8 + (lane >> 3) * 2, col = col0 + local;  // columns col and col + 1
+    const bool live = !producer && col < a.vdim, live1 = !producer && col + 1 < a.vdim;
     const int dim = a.dim, vdim = a.vdim, g = h / (a.heads / a.groups);
-    constexpr int DP = 4 * RPT;             // key rows with padding (zeros: their state stays zero)
+    constexpr int DP = 8 * RPT;             // key rows with padding (zeros: their state stays zero)
     extern __shared__ __align__(16) float sm[];
     const int stage_floats = 2 * SR_TOKENS * DP + SR_TOKENS * a.cols + 2 * SR_TOKENS;  // q, k, v, decay, input scale
     const float skip = a.skip ? a.skip[h] : 0.0f;
@@ -62,11 +63,12 @@ __global__ void __launch_bounds__(256 + SR_PRODUCERS) state_recurrence_kernel(co
     const int first = a.q_start[s], n = a.q_start[s + 1] - first;
     if (n <= 0) return;
     float* slot = a.state + (size_t)a.state_slots[s] * a.slot_stride + (size_t)h * dim * vdim;
-    float S[RPT];
+    float S[RPT], S1[RPT];
 #pragma unroll
     for (int r = 0; r < RPT; ++r) {
-        const int row = (r >> 2) * 16 + part * 4 + (r & 3);
+        const int row = (r >> 2) * 32 + part * 4 + (r & 3);
         S[r] = (live && row < dim) ? slot[(size_t)row * vdim + col] : 0.0f;
+        S1[r] = (live1 && row < dim) ? slot[(size_t)row * vdim + col + 1] : 0.0f;
     }
     const AT* qp = (const AT*)a.q + (size_t)g * dim;
     const AT* kp = (const AT*)a.k + (size_t)g * dim;
@@ -210,40 +212,64 @@ __global__ void __launch_bounds__(256 + SR_PRODUCERS) state_recurrence_kernel(co
             for (int t = 0; t < count; ++t) {
                 const float4* qt = reinterpret_cast<const float4*>(sq + t * DP) + part;
                 const float4* kt = reinterpret_cast<const float4*>(sk + t * DP) + part;
-                const float vt = sv[t * a.cols + local];
-                float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;  // four chains instead of one of dim / 4 links
+                const float2 vt = *reinterpret_cast<const float2*>(sv + t * a.cols + local);
+                float a0 = 0.0f, a1 = 0.0f, a2 = 0.0f, a3 = 0.0f;  // four chains a column instead of one of dim / 8 links
+                float b0 = 0.0f, b1 = 0.0f, b2 = 0.0f, b3 = 0.0f;
                 if (dtp) {
-                    const float decay = sa[t], bv = sb[t] * vt;
+                    const float decay = sa[t], bv0 = sb[t] * vt.x, bv1 = sb[t] * vt.y;
 #pragma unroll
                     for (int j = 0; j < RPT / 4; ++j) {
-                        const float4 k4 = kt[4 * j], q4 = qt[4 * j];
-                        S[4 * j] = fmaf(decay, S[4 * j], k4.x * bv);
-                        S[4 * j + 1] = fmaf(decay, S[4 * j + 1], k4.y * bv);
-                        S[4 * j + 2] = fmaf(decay, S[4 * j + 2], k4.z * bv);
-                        S[4 * j + 3] = fmaf(decay, S[4 * j + 3], k4.w * bv);
+                        const float4 k4 = kt[8 * j], q4 = qt[8 * j];
+                        S[4 * j] = fmaf(decay, S[4 * j], k4.x * bv0);
+                        S[4 * j + 1] = fmaf(decay, S[4 * j + 1], k4.y * bv0);
+                        S[4 * j + 2] = fmaf(decay, S[4 * j + 2], k4.z * bv0);
+                        S[4 * j + 3] = fmaf(decay, S[4 * j + 3], k4.w * bv0);
+                        S1[4 * j] = fmaf(decay, S1[4 * j], k4.x * bv1);
+                        S1[4 * j + 1] = fmaf(decay, S1[4 * j + 1], k4.y * bv1);
+                        S1[4 * j + 2] = fmaf(decay, S1[4 * j + 2], k4.z * bv1);
+                        S1[4 * j + 3] = fmaf(decay, S1[4 * j + 3], k4.w * bv1);
                         a0 = fmaf(S[4 * j], q4.x, a0);
                         a1 = fmaf(S[4 * j + 1], q4.y, a1);
                         a2 = fmaf(S[4 * j + 2], q4.z, a2);
                         a3 = fmaf(S[4 * j + 3], q4.w, a3);
+                        b0 = fmaf(S1[4 * j], q4.x, b0);
+                        b1 = fmaf(S1[4 * j + 1], q4.y, b1);
+                        b2 = fmaf(S1[4 * j + 2], q4.z, b2);
+                        b3 = fmaf(S1[4 * j + 3], q4.w, b3);
                     }
                 } else {
 #pragma unroll
                     for (int j = 0; j < RPT / 4; ++j) {
-                        const float4 k4 = kt[4 * j], q4 = qt[4 * j];
-                        S[4 * j] = fmaf(k4.x, vt, fmaf(-loss, S[4 * j], S[4 * j]));
-                        S[4 * j + 1] = fmaf(k4.y, vt, fmaf(-loss, S[4 * j + 1], S[4 * j + 1]));
-                        S[4 * j + 2] = fmaf(k4.z, vt, fmaf(-loss, S[4 * j + 2], S[4 * j + 2]));
-                        S[4 * j + 3] = fmaf(k4.w, vt, fmaf(-loss, S[4 * j + 3], S[4 * j + 3]));
+                        const float4 k4 = kt[8 * j], q4 = qt[8 * j];
+                        S[4 * j] = fmaf(k4.x, vt.x, fmaf(-loss, S[4 * j], S[4 * j]));
+                        S[4 * j + 1] = fmaf(k4.y, vt.x, fmaf(-loss, S[4 * j + 1], S[4 * j + 1]));
+                        S[4 * j + 2] = fmaf(k4.z, vt.x, fmaf(-loss, S[4 * j + 2], S[4 * j + 2]));
+                        S[4 * j + 3] = fmaf(k4.w, vt.x, fmaf(-loss, S[4 * j + 3], S[4 * j + 3]));
+                        S1[4 * j] = fmaf(k4.x, vt.y, fmaf(-loss, S1[4 * j], S1[4 * j]));
+                        S1[4 * j + 1] = fmaf(k4.y, vt.y, fmaf(-loss, S1[4 * j + 1], S1[4 * j + 1]));
+                        S1[4 * j + 2] = fmaf(k4.z, vt.y, fmaf(-loss, S1[4 * j + 2], S1[4 * j + 2]));
+                        S1[4 * j + 3] = fmaf(k4.w, vt.y, fmaf(-loss, S1[4 * j + 3], S1[4 * j + 3]));
                         a0 = fmaf(S[4 * j], q4.x, a0);
                         a1 = fmaf(S[4 * j + 1], q4.y, a1);
                         a2 = fmaf(S[4 * j + 2], q4.z, a2);
                         a3 = fmaf(S[4 * j + 3], q4.w, a3);
+                        b0 = fmaf(S1[4 * j], q4.x, b0);
+                        b1 = fmaf(S1[4 * j + 1], q4.y, b1);
+                        b2 = fmaf(S1[4 * j + 2], q4.z, b2);
+                        b3 = fmaf(S1[4 * j + 3], q4.w, b3);
                     }
                 }
-                float acc = (a0 + a1) + (a2 + a3);
-                acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-                acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-                if (live && part == 0) op[(row0 + t) * ((size_t)a.heads * vdim)] = fmaf(skip, vt, acc);
+                float acc = (a0 + a1) + (a2 + a3), acc1 = (b0 + b1) + (b2 + b3);
+#pragma unroll
+                for (int o = 1; o < 8; o <<= 1) {
+                    acc += __shfl_xor_sync(0xffffffffu, acc, o);
+                    acc1 += __shfl_xor_sync(0xffffffffu, acc1, o);
+                }
+                if (part == 0) {
+                    float* o_row = op + (row0 + t) * ((size_t)a.heads * vdim);
+                    if (live) o_row[0] = fmaf(skip, vt.x, acc);
+                    if (live1) o_row[1] = fmaf(skip, vt.y, acc1);
+                }
             }
         }
         __syncthreads();
@@ -251,8 +277,9 @@ __global__ void __launch_bounds__(256 + SR_PRODUCERS) state_recurrence_kernel(co
     pdl_trigger();
 #pragma unroll
     for (int r = 0; r < RPT; ++r) {
-        const int row = (r >> 2) * 16 + part * 4 + (r & 3);
+        const int row = (r >> 2) * 32 + part * 4 + (r & 3);
         if (live && row < dim) slot[(size_t)row * vdim + col] = S[r];
+        if (live1 && row < dim) slot[(size_t)row * vdim + col + 1] = S1[r];
     }
 }
 
@@ -269,17 +296,17 @@ static int launch_state_recurrence(const StateRecurrenceArgs& a, int num_seqs, i
     args.bulk = a.dim % epv == 0 && a.vdim % epv == 0 && a.q_ld % epv == 0 && a.k_ld % epv == 0 && a.v_ld % epv == 0 &&
                 (((uintptr_t)a.q | (uintptr_t)a.k | (uintptr_t)a.v) & 15) == 0;
     const dim3 grid(a.heads, num_seqs, (a.vdim + cols - 1) / cols), block(cols * 4 + SR_PRODUCERS);
-    const int rpt = (a.dim + 15) / 16 * 4;  // key rows in runs of 16: four to each of a column's four lanes
+    const int rpt = (a.dim + 31) / 32 * 4;  // key rows in runs of 32: four to each of a column pair's eight lanes
 #define SR_CASE(R)                                                                                                   \
     if (rpt <= R) {                                                                                                  \
-        const size_t smem = (size_t)2 * (2 * SR_TOKENS * 4 * R + SR_TOKENS * cols + 2 * SR_TOKENS) * sizeof(float) + \
+        const size_t smem = (size_t)2 * (2 * SR_TOKENS * 8 * R + SR_TOKENS * cols + 2 * SR_TOKENS) * sizeof(float) + \
                             (size_t)SR_TOKENS * (2 * a.dim + cols) * sizeof(AT);                                      \
         auto kern = state_recurrence_kernel<AT, R>;                                                                  \
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
         launch_kernel(kern, grid, block, smem, stream, args);                                                        \
         return launch_status();                                                                                      \
     }
-    SR_CASE(4) SR_CASE(8) SR_CASE(16) SR_CASE(32) SR_CASE(64)
+    SR_CASE(4) SR_CASE(8) SR_CASE(16) SR_CASE(32)
 #undef SR_CASE
     return SHISO_ERR_SHAPE;
 }
