@@ -136,9 +136,15 @@ SHISO_API int shiso_group_rmsnorm(const void* x, int x_dtype, long long x_ld, co
 
 #define SHISO_CONV_MAX_TAPS 8
 
+#define SHISO_CONV_ROWS 8  // rows a thread walks with the window in registers
+
 // y_t[c] = act(bias[c] + sum_j taps[c, j] * x_{t-(L-1)+j}[c]); inputs before a portion's first row
 // come from the request's slot (its last L-1 inputs, oldest first, float; zeros for a new
-// request).  A thread per (row, channel); the slot is read here and written by the kernel below.
+// request).  A thread per (run of eight rows, channel): where the run lies in one sequence the
+// window moves through registers (a row's inputs are read once, not once per tap; taps and window
+// are kept at the END of arrays of the largest size, zeros before, so that every index is a
+// constant); a run that crosses into another sequence takes its rows one by one.  The slot is
+// read here and written by the kernel below.
 template <typename AT>
 __global__ void causal_conv_kernel(const AT* __restrict__ x, long long x_ld, const float* __restrict__ taps,
                                    const float* __restrict__ bias, const float* __restrict__ state, long long slot_stride,
@@ -146,22 +152,58 @@ __global__ void causal_conv_kernel(const AT* __restrict__ x, long long x_ld, con
                                    const int* __restrict__ state_slots, AT* __restrict__ y, int tokens, int channels, int n_taps,
                                    int silu) {
     pdl_begin();
+    constexpr int M = SHISO_CONV_MAX_TAPS;
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (long long)tokens * channels) return;
-    const int t = (int)(i / channels), c = (int)(i % channels);
-    const int s = seq_of_token[t];
-    const int first = q_start[s];
-    const float* slot = state + (size_t)state_slots[s] * slot_stride;
-    float acc = bias ? bias[c] : 0.0f;
-    for (int j = 0; j < n_taps; ++j) {
-        const int src = t - (n_taps - 1) + j;  // a row of this step, or behind its first row
-        float v;
-        if (src >= first) v = to_f32(x[(size_t)src * x_ld + c]);
-        else v = slot[(size_t)(n_taps - 1 - (first - src)) * channels + c];
-        acc += taps[(size_t)c * n_taps + j] * v;
+    const int runs = (tokens + SHISO_CONV_ROWS - 1) / SHISO_CONV_ROWS;
+    if (i >= (long long)runs * channels) return;
+    const int run = (int)(i / channels), c = (int)(i % channels);
+    const int t0 = run * SHISO_CONV_ROWS, t_end = min(t0 + SHISO_CONV_ROWS, tokens);
+    const float b = bias ? bias[c] : 0.0f;
+    const int off = M - n_taps;  // tap j sits at tp[off + j]: the current row's tap is always tp[M - 1]
+    float tp[M];
+#pragma unroll
+    for (int k = 0; k < M; ++k) tp[k] = k >= off ? taps[(size_t)c * n_taps + (k - off)] : 0.0f;
+    const int s0 = seq_of_token[t0];
+    if (seq_of_token[t_end - 1] == s0) {
+        const int first = q_start[s0];
+        const float* slot = state + (size_t)state_slots[s0] * slot_stride;
+        float w[M - 1];  // w[k], k >= off: the input n_taps - 1 - (k - off) rows before the current one
+#pragma unroll
+        for (int k = 0; k < M - 1; ++k) {
+            w[k] = 0.0f;
+            if (k >= off) {
+                const int src = t0 - (n_taps - 1) + (k - off);
+                w[k] = src >= first ? to_f32(x[(size_t)src * x_ld + c]) : slot[(size_t)(n_taps - 1 - (first - src)) * channels + c];
+            }
+        }
+        for (int t = t0; t < t_end; ++t) {
+            const float xin = to_f32(x[(size_t)t * x_ld + c]);
+            float acc = fmaf(tp[M - 1], xin, b);
+#pragma unroll
+            for (int k = 0; k < M - 1; ++k) acc = fmaf(tp[k], w[k], acc);
+#pragma unroll
+            for (int k = 0; k < M - 2; ++k) w[k] = w[k + 1];
+            w[M - 2] = xin;
+            if (silu) acc = acc / (1.0f + expf(-acc));
+            y[(size_t)t * channels + c] = from_f32<AT>(acc);
+        }
+        return;
     }
-    if (silu) acc = acc / (1.0f + expf(-acc));
-    y[(size_t)t * channels + c] = from_f32<AT>(acc);
+    for (int t = t0; t < t_end; ++t) {
+        const int s = seq_of_token[t];
+        const int first = q_start[s];
+        const float* slot = state + (size_t)state_slots[s] * slot_stride;
+        float acc = b;
+        for (int j = 0; j < n_taps; ++j) {
+            const int src = t - (n_taps - 1) + j;  // a row of this step, or behind its first row
+            float v;
+            if (src >= first) v = to_f32(x[(size_t)src * x_ld + c]);
+            else v = slot[(size_t)(n_taps - 1 - (first - src)) * channels + c];
+            acc = fmaf(taps[(size_t)c * n_taps + j], v, acc);
+        }
+        if (silu) acc = acc / (1.0f + expf(-acc));
+        y[(size_t)t * channels + c] = from_f32<AT>(acc);
+    }
 }
 
 // The slot's new content: the last L-1 inputs of the sequence (rows of this step, and what the
@@ -192,7 +234,8 @@ SHISO_API int shiso_causal_conv(const void* x, long long x_ld, int act_dtype, co
                                 int tokens, int num_seqs, int channels, int n_taps, int silu, cudaStream_t stream) {
     if (tokens <= 0) return SHISO_OK;
     if (n_taps < 2 || n_taps > SHISO_CONV_MAX_TAPS || channels <= 0) return SHISO_ERR_SHAPE;
-    const unsigned blocks = ceil_div_u((long long)tokens * channels, 256), sblocks = ceil_div_u((long long)num_seqs * channels, 256);
+    const unsigned blocks = ceil_div_u((long long)((tokens + SHISO_CONV_ROWS - 1) / SHISO_CONV_ROWS) * channels, 256);
+    const unsigned sblocks = ceil_div_u((long long)num_seqs * channels, 256);
     if (act_dtype == SHISO_F32) {
         launch_kernel(causal_conv_kernel<float>, blocks, 256, 0, stream, (const float*)x, x_ld, taps, bias, (const float*)state,
                       slot_stride, seq_of_token, q_start, state_slots, (float*)y, tokens, channels, n_taps, silu);
