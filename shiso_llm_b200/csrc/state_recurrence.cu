@@ -35,7 +35,13 @@ struct StateRecurrenceArgs {
     int bulk;  // rows may be fetched 16 bytes at a time (widths, strides and addresses allow it)
 };
 
-__device__ __forceinline__ float sr_silu(float z) { return z / (1.0f + expf(-z)); }
+// silu of a projection's output on its way into shared memory.  float rows: the accurate expf and
+// division.  bfloat16 rows: the special-function unit's exponential and reciprocal (relative error
+// about 2^-21, far below the 2^-9 the input was rounded to) - the staging warps repeat this for
+// every CTA of a head, and the accurate forms were most of their instructions.
+template <typename AT> __device__ __forceinline__ float sr_silu(float z);
+template <> __device__ __forceinline__ float sr_silu<float>(float z) { return z / (1.0f + expf(-z)); }
+template <> __device__ __forceinline__ float sr_silu<__nv_bfloat16>(float z) { return __fdividef(z, 1.0f + __expf(-z)); }
 __device__ __forceinline__ void sr_cp16(void* dst, const void* src, bool valid) {
     const int bytes = valid ? 16 : 0;
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src), "r"(bytes) : "memory");
@@ -104,7 +110,7 @@ __global__ void __launch_bounds__(256 + SR_PRODUCERS) state_recurrence_kernel(co
             for (int u = 0; u < U; ++u) {
                 const int i = i0 + u * threads;
                 if (i >= SR_TOKENS * DP) continue;
-                if (a.silu) qv[u] = sr_silu(qv[u]), kv[u] = sr_silu(kv[u]);
+                if (a.silu) qv[u] = sr_silu<AT>(qv[u]), kv[u] = sr_silu<AT>(kv[u]);
                 sq[i] = ok[u] ? qv[u] : 0.0f;
                 sk[i] = ok[u] ? kv[u] : 0.0f;
             }
@@ -122,7 +128,7 @@ __global__ void __launch_bounds__(256 + SR_PRODUCERS) state_recurrence_kernel(co
             for (int u = 0; u < 4; ++u) {
                 const int i = i0 + u * threads;
                 if (i >= SR_TOKENS * a.cols) continue;
-                if (a.silu) vv[u] = sr_silu(vv[u]);
+                if (a.silu) vv[u] = sr_silu<AT>(vv[u]);
                 sv[i] = ok[u] ? vv[u] : 0.0f;
             }
         }
@@ -174,14 +180,14 @@ __global__ void __launch_bounds__(256 + SR_PRODUCERS) state_recurrence_kernel(co
             float qv = 0.0f, kv = 0.0f;
             if (c < dim && t < count) {
                 qv = to_f32(rq[t * dim + c]), kv = to_f32(rk[t * dim + c]);
-                if (a.silu) qv = sr_silu(qv), kv = sr_silu(kv);
+                if (a.silu) qv = sr_silu<AT>(qv), kv = sr_silu<AT>(kv);
             }
             sq[i] = qv;
             sk[i] = kv;
         }
         for (int i = me; i < SR_TOKENS * a.cols; i += threads) {
             float vv = to_f32(rv[i]);  // zeros where the copy was left out
-            if (a.silu) vv = sr_silu(vv);
+            if (a.silu) vv = sr_silu<AT>(vv);
             sv[i] = vv;
         }
         if (dtp && me < count) {
@@ -285,10 +291,11 @@ __global__ void __launch_bounds__(256 + SR_PRODUCERS) state_recurrence_kernel(co
 
 template <typename AT>
 static int launch_state_recurrence(const StateRecurrenceArgs& a, int num_seqs, int sm_count, cudaStream_t stream) {
-    // value columns per CTA: fewer while SMs would stay idle, but at least 32 (every CTA stages and
-    // activates its head's keys and queries itself, so narrow CTAs repeat that work), or what the head has
+    // value columns per CTA: fewer while SMs would stay idle, but at least 16 (every CTA's staging
+    // warps bring and activate its head's keys and queries themselves, so narrow CTAs repeat that
+    // work), or what the head has
     int cols = 64;
-    while (cols > 32 && (long long)a.heads * num_seqs * ((a.vdim + cols - 1) / cols) < sm_count) cols /= 2;
+    while (cols > 16 && (long long)a.heads * num_seqs * ((a.vdim + cols - 1) / cols) < sm_count) cols /= 2;
     while (cols > 8 && cols / 2 >= a.vdim) cols /= 2;
     StateRecurrenceArgs args = a;
     args.cols = cols;
