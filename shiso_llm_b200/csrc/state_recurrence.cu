@@ -142,19 +142,18 @@ __global__ void __launch_bounds__(256 + SR_PRODUCERS) state_recurrence_kernel(co
         }
     };
 
-    // The same by the staging warps alone, with every byte of the sixteen rows in flight at once:
-    // 16-byte cp.async into a raw area of their own, one wait, a barrier among themselves, then the
-    // conversion (and activation) into the stage.  A row costs one trip to memory instead of several.
-    AT* raw = reinterpret_cast<AT*>(sm + 2 * stage_floats);  // [SR_TOKENS][dim] q, the same of k, [SR_TOKENS][cols] v
-    auto stage_rows_bulk = [&](int base, float* st, int me, int threads) {
+    // The same by the staging warps alone, in two halves.  bulk_fetch asks for every byte of sixteen
+    // rows at once (16-byte cp.async into one of two raw areas of their own); bulk_convert, an
+    // iteration later, turns a raw area that has landed into a stage (conversion, activation, the
+    // decays).  The copies of the rows after next are thus on their way while the next rows are
+    // converted and the current ones walked: a row costs no visible trip to memory.
+    const int raw_elems = SR_TOKENS * (2 * dim + a.cols);
+    AT* raw_base = reinterpret_cast<AT*>(sm + 2 * stage_floats);  // two areas: [SR_TOKENS][dim] q, the same of k, [SR_TOKENS][cols] v
+    float z_next = 0.0f, z_cur = 0.0f;  // the step size's logit of this thread's row, fetched with the copies
+    auto bulk_fetch = [&](int base, AT* raw, int me, int threads) {
         constexpr int EPV = 16 / (int)sizeof(AT);  // elements a copy
         const int count = min(SR_TOKENS, n - base);
         const size_t row0 = (size_t)(first + base);
-        float* sq = st;
-        float* sk = sq + SR_TOKENS * DP;
-        float* sv = sk + SR_TOKENS * DP;
-        float* sa = sv + SR_TOKENS * a.cols;
-        float* sb = sa + SR_TOKENS;
         AT* rq = raw;
         AT* rk = rq + SR_TOKENS * dim;
         AT* rv = rk + SR_TOKENS * dim;
@@ -171,10 +170,18 @@ __global__ void __launch_bounds__(256 + SR_PRODUCERS) state_recurrence_kernel(co
             sr_cp16(rv + t * a.cols + c, ok ? vp + (row0 + t) * a.v_ld + c : vp, ok);
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
-        float z = 0.0f;
-        if (dtp && me < count) z = to_f32(dtp[(row0 + me) * a.dt_ld]) + dt_bias;
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
-        asm volatile("bar.sync 1, %0;" ::"r"(threads) : "memory");  // the staging warps among themselves
+        if (dtp && me < count) z_next = to_f32(dtp[(row0 + me) * a.dt_ld]) + dt_bias;
+    };
+    auto bulk_convert = [&](int base, const AT* raw, float* st, int me, int threads, float z) {
+        const int count = min(SR_TOKENS, n - base);
+        float* sq = st;
+        float* sk = sq + SR_TOKENS * DP;
+        float* sv = sk + SR_TOKENS * DP;
+        float* sa = sv + SR_TOKENS * a.cols;
+        float* sb = sa + SR_TOKENS;
+        const AT* rq = raw;
+        const AT* rk = rq + SR_TOKENS * dim;
+        const AT* rv = rk + SR_TOKENS * dim;
         for (int i = me; i < SR_TOKENS * DP; i += threads) {
             const int t = i / DP, c = i - t * DP;
             float qv = 0.0f, kv = 0.0f;
@@ -195,17 +202,29 @@ __global__ void __launch_bounds__(256 + SR_PRODUCERS) state_recurrence_kernel(co
             sb[me] = step;
             sa[me] = expf(-rate * step);
         }
-    };  // (the block's barrier at the end of the sixteen rows also frees the raw area for the next ones)
+    };
 
     stage_rows(0, sm, threadIdx.x, blockDim.x);  // the first rows: everybody
+    const int me = (int)threadIdx.x - workers, stagers = (int)blockDim.x - workers;
+    if (producer && a.bulk && SR_TOKENS < n) bulk_fetch(SR_TOKENS, raw_base + raw_elems, me, stagers);  // rows 16 .. 31 into area 1
     __syncthreads();
     int buf = 0;
     for (int base = 0; base < n; base += SR_TOKENS, buf ^= 1) {
         const int count = min(SR_TOKENS, n - base);
         if (producer) {
-            if (base + SR_TOKENS < n) {
-                if (a.bulk) stage_rows_bulk(base + SR_TOKENS, sm + (buf ^ 1) * stage_floats, threadIdx.x - workers, blockDim.x - workers);
-                else stage_rows(base + SR_TOKENS, sm + (buf ^ 1) * stage_floats, threadIdx.x - workers, blockDim.x - workers);
+            if (base + SR_TOKENS < n) {  // the rows after these: into the other stage
+                float* next_stage = sm + (buf ^ 1) * stage_floats;
+                if (a.bulk) {
+                    // area (buf ^ 1) holds them once this thread's and the other staging threads' copies are done
+                    asm volatile("cp.async.wait_group 0;" ::: "memory");
+                    asm volatile("bar.sync 1, %0;" ::"r"(stagers) : "memory");
+                    z_cur = z_next;
+                    // area buf was converted an iteration ago (the block's barrier lies between): the rows after next go there
+                    if (base + 2 * SR_TOKENS < n) bulk_fetch(base + 2 * SR_TOKENS, raw_base + buf * raw_elems, me, stagers);
+                    bulk_convert(base + SR_TOKENS, raw_base + (buf ^ 1) * raw_elems, next_stage, me, stagers, z_cur);
+                } else {
+                    stage_rows(base + SR_TOKENS, next_stage, me, stagers);
+                }
             }
         } else {
             const float* st = sm + buf * stage_floats;
@@ -307,7 +326,7 @@ static int launch_state_recurrence(const StateRecurrenceArgs& a, int num_seqs, i
 #define SR_CASE(R)                                                                                                   \
     if (rpt <= R) {                                                                                                  \
         const size_t smem = (size_t)2 * (2 * SR_TOKENS * 8 * R + SR_TOKENS * cols + 2 * SR_TOKENS) * sizeof(float) + \
-                            (size_t)SR_TOKENS * (2 * a.dim + cols) * sizeof(AT);                                      \
+                            (size_t)2 * SR_TOKENS * (2 * a.dim + cols) * sizeof(AT);                                  \
         auto kern = state_recurrence_kernel<AT, R>;                                                                  \
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
         launch_kernel(kern, grid, block, smem, stream, args);                                                        \
