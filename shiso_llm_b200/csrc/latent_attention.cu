@@ -8,8 +8,8 @@
 // positions are cut into runs of 32 from position 0; run c belongs to warp c % 8 of share
 // (c / 8) % shares.  A lane scores its own key against the four queries (the cached row is read
 // once for four heads, 16 bytes at a time where the width allows), the run's softmax is folded
-// into the warp's running maximum and sum, and for the values the lanes change roles: lane l sums
-// latent entries l, l + 32, ... over the run's keys.  Warps' results are merged in warp order,
+// into the warp's running maximum and sum, and for the values the lanes change roles: a lane sums
+// a few neighbouring latent entries (one load of up to 16 bytes a key) over the run's keys.  Warps' results are merged in warp order,
 // shares (decode steps at long contexts) through a scratch buffer by a second kernel, in share
 // order.  What is added in which order depends on the row's position and the number of shares
 // only.  Scores, softmax and sums are float.
@@ -39,6 +39,19 @@ template <> struct LaVec<__nv_bfloat16> {
     }
 };
 
+template <typename AT, int E> __device__ __forceinline__ void la_load(const AT* p, float* f) {
+    if constexpr (E == 1) {
+        f[0] = to_f32(p[0]);
+    } else {
+        struct alignas(sizeof(AT) * E) Pack {
+            AT v[E];
+        };
+        const Pack pack = *reinterpret_cast<const Pack*>(p);
+#pragma unroll
+        for (int e = 0; e < E; ++e) f[e] = to_f32(pack.v[e]);
+    }
+}
+
 // RV: latent entries a lane sums (rank <= 32 RV).  VEC: the cached rows are read 16 bytes at a time.
 template <typename AT, int RV, bool VEC>
 __global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(
@@ -50,6 +63,10 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(
     float* sp = sq + LA_HEADS * width;               // [LA_WARPS][LA_HEADS][32] a run's softmax weights
     float* sml = sp + LA_WARPS * LA_HEADS * 32;      // [LA_WARPS][LA_HEADS][2] running maximum and sum
     float* sacc = sml + LA_WARPS * LA_HEADS * 2;     // [LA_WARPS][LA_HEADS][rank]
+    // Latent entries a lane reads at once in the value pass (VEC: as many as a 16-byte load or the
+    // lane's share holds; the rank is then a multiple of it): entry i of a lane is latent entry
+    // (i / E) * 32 E + lane * E + i % E.
+    constexpr int E = VEC ? (RV < LaVec<AT>::N ? RV : LaVec<AT>::N) : 1;
     const int t = blockIdx.x, h0 = blockIdx.y * LA_HEADS, share = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     pdl_wait();
@@ -114,12 +131,15 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(
 #pragma unroll
             for (int g = 0; g < LA_HEADS; ++g) p[g] = wp[g * 32 + key];
 #pragma unroll
-            for (int i = 0; i < RV; ++i) {
-                const int r = lane + 32 * i;
-                if (r < rank) {
-                    const float cv = to_f32(krow[r]);
+            for (int c = 0; c < RV / E; ++c) {
+                const int r0 = c * 32 * E + lane * E;  // this lane's E neighbouring latent entries of the chunk
+                if (r0 < rank) {
+                    float cv[E];
+                    la_load<AT, E>(krow + r0, cv);
 #pragma unroll
-                    for (int g = 0; g < LA_HEADS; ++g) acc[g][i] = fmaf(p[g], cv, acc[g][i]);
+                    for (int e = 0; e < E; ++e)
+#pragma unroll
+                        for (int g = 0; g < LA_HEADS; ++g) acc[g][c * E + e] = fmaf(p[g], cv[e], acc[g][c * E + e]);
                 }
             }
         }
@@ -131,7 +151,7 @@ __global__ void __launch_bounds__(LA_WARPS * 32) latent_attention_kernel(
         if (lane == 0) sml[(warp * LA_HEADS + g) * 2] = m[g], sml[(warp * LA_HEADS + g) * 2 + 1] = l[g];
 #pragma unroll
         for (int i = 0; i < RV; ++i) {
-            const int r = lane + 32 * i;
+            const int r = (i / E) * 32 * E + lane * E + (i % E);
             if (r < rank) sacc[((size_t)warp * LA_HEADS + g) * rank + r] = acc[g][i];
         }
     }
@@ -196,7 +216,8 @@ static int launch_latent_attention(const void* q, const void* cache, const int* 
     const int rv = (rank + 31) / 32;
 #define LA_CASE(R)                                                                                                       \
     if (rv <= R) {                                                                                                       \
-        auto kern = vec ? latent_attention_kernel<AT, R, true> : latent_attention_kernel<AT, R, false>;                  \
+        const bool wide = vec && rank % (R < N ? R : N) == 0;                                                            \
+        auto kern = wide ? latent_attention_kernel<AT, R, true> : latent_attention_kernel<AT, R, false>;                 \
         if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
         launch_kernel(kern, grid, block, smem, stream, (const AT*)q, (const AT*)cache, block_table, table_width, positions, \
                       seq_of_token, (AT*)out, scratch, heads, rank, width, page_size, scale, shares);                    \
