@@ -523,7 +523,7 @@ def ff_part(mlp, width):
 
 
 @pytest.mark.parametrize("backend", BACKENDS)
-@pytest.mark.parametrize("mlp", [{"kind": "dense", "ff": 50}, moe(12, 4, 4, 3, 2.0, 14, 20), moe(7, 2, 1, 1, 1.0, 9, None),
+@pytest.mark.parametrize("mlp", [{"kind": "dense", "ff": 50}, moe(10, 3, 5, 3, 1.75, 14, 20), moe(7, 2, 1, 1, 1.0, 9, None),
                                  moe(6, 6, 2, 2, 0.5, 8, 8), moe(8, 1, 8, 1, 1.0, 12, None)], ids=["dense", "groups", "plain", "all", "one"])
 def test_feed_forwards_alone(backend, mlp):
     for dtype in mixer_dtypes(backend):
